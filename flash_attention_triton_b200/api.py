@@ -1,0 +1,252 @@
+"""Drop-in Python surface of the reference's causal FlashAttention-2 operator.
+
+Mirrors ``src/flash_attention_triton/flash_attention_2.py`` of flash-attention-triton:
+
+* :func:`flash_attention_v2` (reference lines 646-697) — same name, arguments and defaults;
+* :func:`flash_attention_v2_custom` (700-790) — same signature; the tile/warp knobs of the
+  config are ignored (there is no Triton here), only its ``SEQUENCE_PARALLEL`` flag survives
+  as the deterministic switch;
+* :class:`FlashAttentionV2Function` (280-384) — ``apply(q, k, v, softmax_scale, deterministic)``
+  returning five gradients ``(dq, dk, dv, None, None)``;
+* :class:`KernelsConfigV2`, :func:`init_to_zero_v2` (``_configurators_v2.py:9-93``).
+
+Differences, all deliberate: fp16 and bf16 inputs run natively (the reference casts
+everything to fp16, lines 316/379); other float dtypes are cast to fp16 exactly as the
+reference does.  Head dimension must be 32, 64 or 128 and ``seqlen_q == seqlen_k``.
+Everything runs through the C library on the tensors' CUDA device; there is no fallback.
+"""
+
+from __future__ import annotations
+
+import math
+from collections.abc import Callable
+from dataclasses import dataclass
+from typing import Any
+
+import torch
+
+from . import _lib
+
+_SUPPORTED_HEAD_DIMS = (32, 64, 128)
+
+
+# ------------------------------------------------------------------ host launch wrappers
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float16:
+        return _lib.FA2_DTYPE_FP16
+    if dtype == torch.bfloat16:
+        return _lib.FA2_DTYPE_BF16
+    raise AssertionError("Supports only fp16 and bf16 compute dtypes")
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _flash_attention_forward(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float | None
+) -> tuple[torch.Tensor, torch.Tensor, float]:
+    """Validate, allocate O and LSE, launch ``fa2_fwd``.
+
+    Counterpart of ``_flash_attention_forward`` (reference lines 61-144): the same asserts on
+    shapes / device / dtype, ``softmax_scale or 1/sqrt(d)`` (so 0.0 means "default"), but
+    LSE is an unpadded ``[B, H, N]`` fp32 tensor and no scratch buffer exists.
+    """
+    batch, nheads, seqlen_q, headdim = q.shape
+    seqlen_k = k.shape[2]
+    assert k.shape == (batch, nheads, seqlen_k, headdim)
+    assert v.shape == (batch, nheads, seqlen_k, headdim)
+    assert q.is_cuda and k.is_cuda and v.is_cuda, "All tensors must reside on CUDA device"
+    assert q.dtype == k.dtype == v.dtype, "All tensors must be the same type"
+    if headdim not in _SUPPORTED_HEAD_DIMS:
+        raise ValueError(f"head dimension {headdim} is not supported (use one of {_SUPPORTED_HEAD_DIMS})")
+    if seqlen_q != seqlen_k:
+        raise ValueError("seqlen_q must equal seqlen_k (causal self-attention)")
+    softmax_scale = softmax_scale or 1.0 / math.sqrt(headdim)
+    output = torch.empty_like(q)
+    lse = torch.empty((batch, nheads, seqlen_q), device=q.device, dtype=torch.float32)
+    with torch.cuda.device(q.device):
+        _lib.check(
+            "fa2_fwd",
+            _lib.lib().fa2_fwd(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(), lse.data_ptr(),
+                batch, nheads, seqlen_q, headdim, _dtype_code(q.dtype), float(softmax_scale),
+                _stream(q),
+            ),
+        )
+    return output, lse, softmax_scale
+
+
+def _flash_attention_backward(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    output: torch.Tensor,
+    lse: torch.Tensor,
+    dq: torch.Tensor,
+    dk: torch.Tensor,
+    dv: torch.Tensor,
+    d_output: torch.Tensor,
+    softmax_scale: float,
+    deterministic: bool,
+) -> None:
+    """Launch ``fa2_bwd_preprocess`` and ``fa2_bwd``.
+
+    Counterpart of ``_flash_attention_backward`` (reference lines 147-277).  The fp32
+    ``dq_accum`` workspace exists only in the non-deterministic mode; the deterministic mode
+    writes dQ once, already rounded.
+    """
+    batch, nheads, seqlen_q, headdim = q.shape
+    if not d_output.is_contiguous():
+        d_output = d_output.contiguous()
+    assert lse.shape == (batch, nheads, seqlen_q)
+    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and output.is_contiguous()
+    assert dq.is_contiguous() and dk.is_contiguous() and dv.is_contiguous()
+    lib = _lib.lib()
+    code = _dtype_code(q.dtype)
+    with torch.cuda.device(q.device):
+        stats_bytes = lib.fa2_rowstats_bytes(batch, nheads, seqlen_q)
+        rowstats = torch.empty(stats_bytes // 4, device=q.device, dtype=torch.float32)
+        _lib.check(
+            "fa2_bwd_preprocess",
+            lib.fa2_bwd_preprocess(
+                output.data_ptr(), d_output.data_ptr(), lse.data_ptr(), rowstats.data_ptr(),
+                batch, nheads, seqlen_q, headdim, code, _stream(q),
+            ),
+        )
+        ws_bytes = lib.fa2_bwd_workspace_bytes(batch, nheads, seqlen_q, headdim, int(deterministic))
+        dq_accum = (
+            torch.empty(ws_bytes // 4, device=q.device, dtype=torch.float32) if ws_bytes else None
+        )
+        _lib.check(
+            "fa2_bwd",
+            lib.fa2_bwd(
+                q.data_ptr(), k.data_ptr(), v.data_ptr(), d_output.data_ptr(), rowstats.data_ptr(),
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                dq_accum.data_ptr() if dq_accum is not None else None,
+                batch, nheads, seqlen_q, headdim, code, float(softmax_scale), int(deterministic),
+                _stream(q),
+            ),
+        )
+
+
+# ------------------------------------------------------------------ autograd integration
+def _compute_dtype(dtype: torch.dtype) -> torch.dtype:
+    # fp16 / bf16 run natively; everything else takes the reference's route (cast to fp16,
+    # reference line 316).
+    return dtype if dtype in (torch.float16, torch.bfloat16) else torch.float16
+
+
+class FlashAttentionV2Function(torch.autograd.Function):
+    """Autograd function for causal FlashAttention-2 (reference lines 280-384)."""
+
+    @staticmethod
+    def forward(ctx: Any, q, k, v, softmax_scale, deterministic):  # noqa: ANN001
+        initial_dtype = q.dtype
+        cdtype = _compute_dtype(q.dtype)
+        q, k, v = [t.contiguous().to(cdtype) for t in (q, k, v)]
+        output, lse, ctx.softmax_scale = _flash_attention_forward(q, k, v, softmax_scale)
+        ctx.save_for_backward(q, k, v, output, lse)
+        ctx.deterministic = bool(deterministic)
+        return output.contiguous().to(initial_dtype)
+
+    @staticmethod
+    def backward(ctx: Any, d_output):  # noqa: ANN001
+        q, k, v, output, lse = ctx.saved_tensors
+        dq = torch.empty_like(q)
+        dk = torch.empty_like(k)
+        dv = torch.empty_like(v)
+        _flash_attention_backward(
+            q, k, v, output, lse, dq, dk, dv, d_output.to(q.dtype), ctx.softmax_scale,
+            ctx.deterministic,
+        )
+        return dq, dk, dv, None, None
+
+
+# ------------------------------------------------------------------ configuration shim
+@dataclass(frozen=True)
+class KernelsConfigV2:
+    """Name-compatible stand-in for the reference's kernel configuration container.
+
+    Same fields as ``_configurators_v2.py:9-38``.  Tile sizes, warp counts and stages have
+    no meaning for the hand-written sm_100a kernels and are ignored; the only information
+    used is whether the first backward config asks for ``SEQUENCE_PARALLEL`` (atomic dQ,
+    non-deterministic) or not (deterministic), as in the reference's tables (lines 570-589).
+    """
+
+    block_rows_size: int
+    block_cols_size: int
+    min_block_headdim: int
+    max_headdim: int
+    seqlen_cache_divisor: int
+    min_warps: int
+    max_warps: int
+    num_stages: int
+    backward_autotune_configs: list
+
+    def is_deterministic(self) -> bool:
+        if not self.backward_autotune_configs:
+            return True
+        first = self.backward_autotune_configs[0]
+        kwargs = getattr(first, "kwargs", first if isinstance(first, dict) else {})
+        return not bool(kwargs.get("SEQUENCE_PARALLEL", False))
+
+
+def init_to_zero_v2(name: str) -> Callable[[dict[str, torch.Tensor]], torch.Tensor]:
+    """Pre-hook factory kept for source compatibility (``_configurators_v2.py:81-93``)."""
+    return lambda nargs: nargs[name].zero_()
+
+
+# ------------------------------------------------------------------ public API
+def _check_device(q: torch.Tensor) -> None:
+    assert q.is_cuda, "All tensors must reside on CUDA device"
+    cc = torch.cuda.get_device_capability(q.device)
+    if cc[0] != 10:
+        raise RuntimeError(
+            f"compute capability {cc} is not supported: this library targets B200 (sm_100a) only"
+        )
+
+
+def flash_attention_v2(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: float | None = None,
+    deterministic: bool = False,
+) -> torch.Tensor:
+    """Causal FlashAttention-2 on B200; same contract as the reference (lines 646-697).
+
+    Args:
+        q, k, v: ``(batch, nheads, seqlen, headdim)`` CUDA tensors of one float dtype.
+        softmax_scale: scaling factor (default and 0.0: ``1/sqrt(headdim)``).
+        deterministic: use the backward whose dQ has a fixed summation order (bit-identical
+            across runs and across batch x head partitionings) instead of fp32 atomics.
+
+    Returns:
+        Attention output, same shape and dtype as ``q``.
+    """
+    _check_device(q)
+    return FlashAttentionV2Function.apply(q, k, v, softmax_scale, deterministic)
+
+
+def flash_attention_v2_custom(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    softmax_scale: float | None,
+    kernels_configs: dict[tuple[int, int], KernelsConfigV2],
+) -> torch.Tensor:
+    """Same signature as the reference (lines 700-790): config looked up by compute capability.
+
+    Raises ``ValueError`` when the current device's capability has no entry, as the
+    reference does (lines 775-779).
+    """
+    _check_device(q)
+    cc = torch.cuda.get_device_capability(q.device)
+    if cc not in kernels_configs:
+        raise ValueError(
+            f"Missing kernel configuration for compute capability {cc}. "
+            "KernelsConfig must be provided for the current GPU architecture"
+        )
+    deterministic = kernels_configs[cc].is_deterministic()
+    return FlashAttentionV2Function.apply(q, k, v, softmax_scale, deterministic)

@@ -1,0 +1,740 @@
+// Causal attention backward for sm_100a.
+//
+// Replaces _backward_kernel_one_col_block and its launcher
+// (src/flash_attention_triton/_triton_kernels_v2.py:192-529 of the reference).  Per
+// (KV tile j, Q tile i >= j) the maths is that of lines 312-343 there:
+//     S = Q K^T, P = exp(scale*S - lse), dP = dO V^T, dS = P o (dP - delta) * scale,
+//     dV += P^T dO, dK += dS^T Q, dQ += dS K.
+//
+// bwd_dkdv_kernel (one CTA per KV tile) works on the TRANSPOSED score tile so that everything
+// a later MMA consumes as its A operand already sits in tensor memory with kv rows on lanes:
+//     St  = K  Q_i^T      (smem x smem)  -> tensor memory, 128 columns
+//     dPt = V  dO_i^T     (smem x smem)  -> tensor memory, 128 columns
+//     dV += Pt  dO_i      (tmem x smem)     Pt  = 16-bit P^T written over St by the compute warps
+//     dK += dSt Q_i       (tmem x smem)     dSt = 16-bit dS^T written over dPt
+//     dQ_i = dS K         (smem x smem)     fused variant only: dS^T also goes to shared memory,
+//                                           the tile lands over dPt and is added to the fp32
+//                                           workspace with vector atomics
+// bwd_dq_kernel (one CTA per Q tile, deterministic path) recomputes S and dP untransposed and
+// accumulates dQ_i over ascending j in tensor memory, so each dQ tile has one owner and one
+// summation order.
+//
+// lse*log2(e) and delta of a Q tile arrive in shared memory as one 1 KiB bulk copy from the
+// tile-blocked rowstats array; padded rows carry lse = +inf, which makes their P exactly 0.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace fa2 {
+namespace {
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(dst_smem),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+
+// Tensor-memory column of the 16-bit operand for MMA step k (16 of the 128 reduction indices):
+// compute group 0 packs indices 0..63 into columns 0..31 of the region, group 1 packs indices
+// 64..127 into columns 64..95 (each group only overwrites columns it has already read).
+__device__ __forceinline__ uint32_t packed_col(int k) { return (k < 4) ? k * 8 : 64 + (k - 4) * 8; }
+
+// Epilogue helper: one warp converts its 32 rows of a [128, D] fp32 accumulator to 16 bits,
+// stages them swizzled in `stage` (a free tile buffer) and stores them with one TMA per chunk.
+template <int D, bool BF16>
+__device__ __forceinline__ void store_rows_16bit(uint32_t tmem_row_addr, uint8_t* stage, int warp4,
+                                                 int lane, const CUtensorMap* map, int row_base,
+                                                 int bh, int N) {
+  using T = Tile<D>;
+  const int r = warp4 * 32 + lane;
+#pragma unroll
+  for (int c0 = 0; c0 < D; c0 += 32) {
+    uint32_t v[32];
+    tmem_ld_x32(tmem_row_addr + c0, v);
+    tmem_wait_ld();
+    const int chunk = c0 / T::kChunkElems;
+    const int piece0 = (c0 % T::kChunkElems) / 8;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      uint4 val;
+      val.x = pack2<BF16>(__uint_as_float(v[8 * p + 0]), __uint_as_float(v[8 * p + 1]));
+      val.y = pack2<BF16>(__uint_as_float(v[8 * p + 2]), __uint_as_float(v[8 * p + 3]));
+      val.z = pack2<BF16>(__uint_as_float(v[8 * p + 4]), __uint_as_float(v[8 * p + 5]));
+      val.w = pack2<BF16>(__uint_as_float(v[8 * p + 6]), __uint_as_float(v[8 * p + 7]));
+      *reinterpret_cast<uint4*>(stage + chunk * T::kChunkTileBytes +
+                                swizzled_offset<D>(r, piece0 + p)) = val;
+    }
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && row_base + warp4 * 32 < N) {
+    for (int ch = 0; ch < T::kChunks; ++ch)
+      tma_store_3d(map, ch * T::kChunkElems, row_base + warp4 * 32, bh,
+                   smem_u32(stage + ch * T::kChunkTileBytes + warp4 * 32 * T::kRowBytes));
+    tma_store_commit();
+    tma_store_wait_all();
+  }
+}
+
+// =========================================================================================
+// dK / dV (+ fused dQ) kernel
+// =========================================================================================
+template <int D, bool FUSE>
+struct DkdvCfg {
+  using T = Tile<D>;
+  static constexpr int kStages = 2;  // Q (+rowstats) ring and dO ring
+  static constexpr int kThreads = FUSE ? 512 : 384;
+  static constexpr int kMmaWarp = FUSE ? 12 : 8;
+  static constexpr int kLoadWarp = kMmaWarp + 1;
+  static constexpr int kOffK = 0;
+  static constexpr int kOffV = kOffK + T::kTileBytes;
+  static constexpr int kOffQ = kOffV + T::kTileBytes;
+  static constexpr int kOffDO = kOffQ + kStages * T::kTileBytes;
+  static constexpr int kOffDS = kOffDO + kStages * T::kTileBytes;  // [2][128 kv][64 q] 16-bit
+  static constexpr int kOffStats = kOffDS + (FUSE ? 32768 : 0);    // [kStages][256] fp32
+  static constexpr int kOffBar = kOffStats + kStages * 1024;
+  static constexpr int kBarKV = 0;
+  static constexpr int kBarQFull = 1;                      // kStages
+  static constexpr int kBarQEmpty = kBarQFull + kStages;   // kStages
+  static constexpr int kBarDOFull = kBarQEmpty + kStages;  // kStages
+  static constexpr int kBarDOEmpty = kBarDOFull + kStages;
+  static constexpr int kBarStFull = kBarDOEmpty + kStages;
+  static constexpr int kBarDptFull = kBarStFull + 1;
+  static constexpr int kBarPtReady = kBarDptFull + 1;   // 256 arrivals
+  static constexpr int kBarDsReady = kBarPtReady + 1;   // 256 arrivals
+  static constexpr int kBarDqFull = kBarDsReady + 1;
+  static constexpr int kBarDqDrained = kBarDqFull + 1;  // 128 arrivals
+  static constexpr int kBarDone = kBarDqDrained + 1;
+  static constexpr int kNumBars = kBarDone + 1;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
+  static constexpr int kColSt = 0;
+  static constexpr int kColDpt = 128;  // dQ (fused) reuses these columns
+  static constexpr int kColDV = 256;
+  static constexpr int kColDK = 256 + D;
+  static constexpr int kTmemCols = 512;
+};
+
+enum BwdSite {
+  kBSiteLoadQ = 32,
+  kBSiteLoadDO,
+  kBSiteMmaKV,
+  kBSiteMmaQ,
+  kBSiteMmaDO,
+  kBSiteMmaPt,
+  kBSiteMmaDs,
+  kBSiteMmaDrain,
+  kBSiteCmpQ,
+  kBSiteCmpSt,
+  kBSiteCmpDpt,
+  kBSiteCmpDone,
+  kBSiteRedDq,
+  kBSiteAlign
+};
+
+template <int D, bool BF16, bool FUSE>
+__global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
+    bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                    const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                    const __grid_constant__ CUtensorMap tdk,
+                    const __grid_constant__ CUtensorMap tdv, const float* __restrict__ rowstats,
+                    float* __restrict__ dq_accum, int N, float scale, float scale_log2,
+                    int* status) {
+  using C = DkdvCfg<D, FUSE>;
+  using T = Tile<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  if (smem_base & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, 0x20000 | kBSiteAlign);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_base + C::kOffBar + 8u * i; };
+
+  const int ntiles = (N + 127) >> 7;
+  const int jt = blockIdx.x;  // KV tile; tile 0 has the most Q tiles and is scheduled first
+  const int bh = blockIdx.y;
+  const int nq = ntiles - jt;  // Q tiles jt .. ntiles-1
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(C::kBarKV), 1);
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(bar(C::kBarQFull + i), 1);
+      mbar_init(bar(C::kBarQEmpty + i), 1);
+      mbar_init(bar(C::kBarDOFull + i), 1);
+      mbar_init(bar(C::kBarDOEmpty + i), 1);
+    }
+    mbar_init(bar(C::kBarStFull), 1);
+    mbar_init(bar(C::kBarDptFull), 1);
+    mbar_init(bar(C::kBarPtReady), 256);
+    mbar_init(bar(C::kBarDsReady), 256);
+    mbar_init(bar(C::kBarDqFull), 1);
+    mbar_init(bar(C::kBarDqDrained), 128);
+    mbar_init(bar(C::kBarDone), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == C::kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtx w{abort_flag, status};
+
+  if (warp >= C::kMmaWarp) {
+    // ---------------------------------------------------------------- producer / MMA group
+    if (warp == C::kLoadWarp && lane == 0) {
+      prefetch_tensormap(&tq);
+      prefetch_tensormap(&tk);
+      prefetch_tensormap(&tv);
+      prefetch_tensormap(&tdo);
+      mbar_arrive_expect_tx(bar(C::kBarKV), 2 * T::kTileBytes);
+      for (int ch = 0; ch < T::kChunks; ++ch) {
+        tma_load_3d(smem_base + C::kOffK + ch * T::kChunkTileBytes, &tk, ch * T::kChunkElems,
+                    jt * 128, bh, bar(C::kBarKV));
+        tma_load_3d(smem_base + C::kOffV + ch * T::kChunkTileBytes, &tv, ch * T::kChunkElems,
+                    jt * 128, bh, bar(C::kBarKV));
+      }
+      for (int ii = 0; ii < nq; ++ii) {
+        const int s = ii % C::kStages, ph = (ii / C::kStages) & 1;
+        const int qt = jt + ii;
+        if (!mbar_wait(bar(C::kBarQEmpty + s), ph ^ 1, w, kBSiteLoadQ)) break;
+        mbar_arrive_expect_tx(bar(C::kBarQFull + s), T::kTileBytes + 1024);
+        for (int ch = 0; ch < T::kChunks; ++ch)
+          tma_load_3d(smem_base + C::kOffQ + s * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
+                      ch * T::kChunkElems, qt * 128, bh, bar(C::kBarQFull + s));
+        bulk_load_1d(smem_base + C::kOffStats + s * 1024,
+                     rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024,
+                     bar(C::kBarQFull + s));
+        if (!mbar_wait(bar(C::kBarDOEmpty + s), ph ^ 1, w, kBSiteLoadDO)) break;
+        mbar_arrive_expect_tx(bar(C::kBarDOFull + s), T::kTileBytes);
+        for (int ch = 0; ch < T::kChunks; ++ch)
+          tma_load_3d(smem_base + C::kOffDO + s * T::kTileBytes + ch * T::kChunkTileBytes, &tdo,
+                      ch * T::kChunkElems, qt * 128, bh, bar(C::kBarDOFull + s));
+      }
+    } else if (warp == C::kMmaWarp && lane == 0) {
+      constexpr uint32_t idesc_t = make_idesc(128, 128, BF16, false, false);   // St, dPt
+      constexpr uint32_t idesc_acc = make_idesc(128, D, BF16, false, true);    // dV, dK
+      constexpr uint32_t idesc_dq = make_idesc(128, D, BF16, true, true);      // dQ
+      const uint32_t ka = smem_base + C::kOffK, va = smem_base + C::kOffV;
+      // D[128 kv, 128 q] = A[kv, d] * B[q, d]^T, both K-major
+      auto issue_t = [&](uint32_t col, uint32_t a_base, uint32_t b_base) {
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off =
+              (k / T::kKStepsPerChunk) * T::kChunkTileBytes + (k % T::kKStepsPerChunk) * 32;
+          mma_ss(tmem_base + col, make_smem_desc(a_base + off, 16, T::kAtomBytes, T::kSwizzleMode),
+                 make_smem_desc(b_base + off, 16, T::kAtomBytes, T::kSwizzleMode), idesc_t, k > 0);
+        }
+      };
+      // D[128 kv, D] += A[kv, q](tmem, 16-bit) * B[q, d] (MN-major tile of Q or dO)
+      auto issue_acc = [&](uint32_t col_d, uint32_t col_a, uint32_t b_base, bool accumulate) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_ts(tmem_base + col_d, tmem_base + col_a + packed_col(k),
+                 make_smem_desc(b_base + k * 2 * T::kAtomBytes, T::kChunkTileBytes, T::kAtomBytes,
+                                T::kSwizzleMode),
+                 idesc_acc, (accumulate || k > 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(bar(C::kBarKV), 0, w, kBSiteMmaKV) &&
+                mbar_wait(bar(C::kBarQFull + 0), 0, w, kBSiteMmaQ);
+      if (ok) {
+        issue_t(C::kColSt, ka, smem_base + C::kOffQ);
+        mma_commit(bar(C::kBarStFull));
+        ok = mbar_wait(bar(C::kBarDOFull + 0), 0, w, kBSiteMmaDO);
+      }
+      if (ok) {
+        issue_t(C::kColDpt, va, smem_base + C::kOffDO);
+        mma_commit(bar(C::kBarDptFull));
+      }
+      for (int ii = 0; ok && ii < nq; ++ii) {
+        const int s = ii % C::kStages;
+        const int s1 = (ii + 1) % C::kStages, ph1 = ((ii + 1) / C::kStages) & 1;
+        const uint32_t qa = smem_base + C::kOffQ + s * T::kTileBytes;
+        const uint32_t doa = smem_base + C::kOffDO + s * T::kTileBytes;
+        if (!(ok = mbar_wait(bar(C::kBarPtReady), ii & 1, w, kBSiteMmaPt))) break;
+        tc_fence_after();
+        issue_acc(C::kColDV, C::kColSt, doa, ii > 0);  // dV += Pt dO_i
+        mma_commit(bar(C::kBarDOEmpty + s));
+        if (ii + 1 < nq) {
+          if (!(ok = mbar_wait(bar(C::kBarQFull + s1), ph1, w, kBSiteMmaQ))) break;
+          issue_t(C::kColSt, ka, smem_base + C::kOffQ + s1 * T::kTileBytes);  // St(i+1)
+          mma_commit(bar(C::kBarStFull));
+        }
+        if (!(ok = mbar_wait(bar(C::kBarDsReady), ii & 1, w, kBSiteMmaDs))) break;
+        tc_fence_after();
+        issue_acc(C::kColDK, C::kColDpt, qa, ii > 0);  // dK += dSt Q_i
+        mma_commit(bar(C::kBarQEmpty + s));
+        if constexpr (FUSE) {
+          // dQ_i[128 q, D] = dS[q, kv] * K[kv, d]: A = dS^T tile in smem (q contiguous ->
+          // MN-major), B = K tile (d contiguous -> MN-major); 16 kv rows per MMA.
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_ss(tmem_base + C::kColDpt,
+                   make_smem_desc(smem_base + C::kOffDS + k * 2048, 16384, 1024, kSwizzle128B),
+                   make_smem_desc(ka + k * 2 * T::kAtomBytes, T::kChunkTileBytes, T::kAtomBytes,
+                                  T::kSwizzleMode),
+                   idesc_dq, k > 0);
+          mma_commit(bar(C::kBarDqFull));
+        }
+        if (ii + 1 < nq) {
+          if constexpr (FUSE) {
+            if (!(ok = mbar_wait(bar(C::kBarDqDrained), ii & 1, w, kBSiteMmaDrain))) break;
+            tc_fence_after();
+          }
+          if (!(ok = mbar_wait(bar(C::kBarDOFull + s1), ph1, w, kBSiteMmaDO))) break;
+          issue_t(C::kColDpt, va, smem_base + C::kOffDO + s1 * T::kTileBytes);  // dPt(i+1)
+          mma_commit(bar(C::kBarDptFull));
+        }
+      }
+      if (ok) mma_commit(bar(C::kBarDone));
+    }
+    __syncwarp();
+  } else if (FUSE && warp >= 8) {
+    // ---------------------------------------------------------------- dQ reduction group
+    const int w4 = warp & 3;
+    const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
+    for (int ii = 0; ii < nq; ++ii) {
+      if (!mbar_wait_warp(bar(C::kBarDqFull), ii & 1, w, kBSiteRedDq)) break;
+      tc_fence_after();
+      const int qt = jt + ii;
+      float* dst = dq_accum + (((static_cast<size_t>(bh) * ntiles + qt) * 4 + w4) * (D / 4)) * 128 +
+                   lane * 4;
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 64) {
+        uint32_t v[64];
+        tmem_ld_x32(tmem_base + lane_base + C::kColDpt + c0, v);
+        if (D > 32) tmem_ld_x32(tmem_base + lane_base + C::kColDpt + c0 + 32, v + 32);
+        tmem_wait_ld();
+        if (c0 + 64 >= D) {  // whole tile is in registers: the MMA warp may overwrite it
+          tc_fence_before();
+          mbar_arrive(bar(C::kBarDqDrained));
+        }
+#pragma unroll
+        for (int k = 0; k < (D > 32 ? 16 : 8); ++k)
+          red_add_v4(dst + (c0 / 4 + k) * 128, __uint_as_float(v[4 * k]),
+                     __uint_as_float(v[4 * k + 1]), __uint_as_float(v[4 * k + 2]),
+                     __uint_as_float(v[4 * k + 3]));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- compute groups
+    const int wg = warp >> 2;  // 0: score columns (q) 0..63, 1: 64..127
+    const int w4 = warp & 3;
+    const int r = w4 * 32 + lane;  // kv row in the tile = tensor-memory lane
+    const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
+    const uint32_t tSt = tmem_base + lane_base + C::kColSt + wg * 64;
+    const uint32_t tDpt = tmem_base + lane_base + C::kColDpt + wg * 64;
+    bool ok = true;
+    for (int ii = 0; ii < nq; ++ii) {
+      const int s = ii % C::kStages, ph = (ii / C::kStages) & 1;
+      const float* stats = reinterpret_cast<const float*>(smem + C::kOffStats + s * 1024);
+      const float4* lse2 = reinterpret_cast<const float4*>(stats + wg * 64);
+      const float4* dlt = reinterpret_cast<const float4*>(stats + 128 + wg * 64);
+      if (!(ok = mbar_wait_warp(bar(C::kBarQFull + s), ph, w, kBSiteCmpQ))) break;
+      if (!(ok = mbar_wait_warp(bar(C::kBarStFull), ii & 1, w, kBSiteCmpSt))) break;
+      tc_fence_after();
+      float p[64];
+      {
+        uint32_t sr[64];
+        tmem_ld_x32(tSt, sr);
+        tmem_ld_x32(tSt + 32, sr + 32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l = lse2[c4];
+          p[4 * c4 + 0] = ex2(fmaf(__uint_as_float(sr[4 * c4 + 0]), scale_log2, -l.x));
+          p[4 * c4 + 1] = ex2(fmaf(__uint_as_float(sr[4 * c4 + 1]), scale_log2, -l.y));
+          p[4 * c4 + 2] = ex2(fmaf(__uint_as_float(sr[4 * c4 + 2]), scale_log2, -l.z));
+          p[4 * c4 + 3] = ex2(fmaf(__uint_as_float(sr[4 * c4 + 3]), scale_log2, -l.w));
+        }
+      }
+      if (ii == 0) {  // diagonal tile: keep q >= kv
+#pragma unroll
+        for (int c = 0; c < 64; ++c) p[c] = (wg * 64 + c >= r) ? p[c] : 0.f;
+      }
+      {
+        uint32_t pk[32];
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pk[c] = pack2<BF16>(p[2 * c], p[2 * c + 1]);
+        tmem_st_x32(tSt, pk);  // columns wg*64 .. wg*64+31 of the St region
+        tmem_wait_st();
+      }
+      tc_fence_before();
+      mbar_arrive(bar(C::kBarPtReady));
+
+      if (!(ok = mbar_wait_warp(bar(C::kBarDptFull), ii & 1, w, kBSiteCmpDpt))) break;
+      tc_fence_after();
+      uint32_t dsk[32];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t dp[32];
+        tmem_ld_x32(tDpt + 32 * h, dp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c4 = 0; c4 < 8; ++c4) {
+          const float4 dl = dlt[8 * h + c4];
+          const int c = 32 * h + 4 * c4;
+          const float d0 = p[c + 0] * (__uint_as_float(dp[4 * c4 + 0]) - dl.x) * scale;
+          const float d1 = p[c + 1] * (__uint_as_float(dp[4 * c4 + 1]) - dl.y) * scale;
+          const float d2 = p[c + 2] * (__uint_as_float(dp[4 * c4 + 2]) - dl.z) * scale;
+          const float d3 = p[c + 3] * (__uint_as_float(dp[4 * c4 + 3]) - dl.w) * scale;
+          dsk[16 * h + 2 * c4] = pack2<BF16>(d0, d1);
+          dsk[16 * h + 2 * c4 + 1] = pack2<BF16>(d2, d3);
+        }
+      }
+      tmem_st_x32(tDpt, dsk);  // columns 128 + wg*64 .. +31
+      if constexpr (FUSE) {
+        uint8_t* ds_tile = smem + C::kOffDS + wg * 16384;
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc)
+          *reinterpret_cast<uint4*>(ds_tile + swizzled_offset_128B(r, pc)) =
+              make_uint4(dsk[4 * pc], dsk[4 * pc + 1], dsk[4 * pc + 2], dsk[4 * pc + 3]);
+        fence_proxy_async_smem();
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(C::kBarDsReady));
+    }
+    // epilogue: group 0 stores dV, group 1 stores dK, staged through the idle dO / Q buffers
+    if (ok && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
+      tc_fence_after();
+      if (wg == 0)
+        store_rows_16bit<D, BF16>(tmem_base + lane_base + C::kColDV, smem + C::kOffDO, w4, lane,
+                                  &tdv, jt * 128, bh, N);
+      else
+        store_rows_16bit<D, BF16>(tmem_base + lane_base + C::kColDK, smem + C::kOffQ, w4, lane,
+                                  &tdk, jt * 128, bh, N);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == C::kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// =========================================================================================
+// dQ kernel (deterministic path): one CTA per Q tile, KV tiles in ascending order
+// =========================================================================================
+template <int D>
+struct DqCfg {
+  using T = Tile<D>;
+  static constexpr int kStages = 2;  // K ring and V ring
+  static constexpr int kThreads = 384;
+  static constexpr int kMmaWarp = 8;
+  static constexpr int kLoadWarp = 9;
+  static constexpr int kOffQ = 0;
+  static constexpr int kOffDO = kOffQ + T::kTileBytes;
+  static constexpr int kOffK = kOffDO + T::kTileBytes;
+  static constexpr int kOffV = kOffK + kStages * T::kTileBytes;
+  static constexpr int kOffStats = kOffV + kStages * T::kTileBytes;  // [256] fp32
+  static constexpr int kOffBar = kOffStats + 1024;
+  static constexpr int kBarQ = 0;  // Q, dO and rowstats
+  static constexpr int kBarKFull = 1;
+  static constexpr int kBarKEmpty = kBarKFull + kStages;
+  static constexpr int kBarVFull = kBarKEmpty + kStages;
+  static constexpr int kBarVEmpty = kBarVFull + kStages;
+  static constexpr int kBarSFull = kBarVEmpty + kStages;
+  static constexpr int kBarDpFull = kBarSFull + 1;
+  static constexpr int kBarDsReady = kBarDpFull + 1;  // 256 arrivals
+  static constexpr int kBarDone = kBarDsReady + 1;
+  static constexpr int kNumBars = kBarDone + 1;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
+  static constexpr int kColS = 0;
+  static constexpr int kColDp = 128;  // dS (16-bit) is written over dP
+  static constexpr int kColDQ = 256;
+  static constexpr int kTmemCols = 512;
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
+    bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                  const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
+                  const __grid_constant__ CUtensorMap tdq, const float* __restrict__ rowstats, int N,
+                  float scale, float scale_log2, int* status) {
+  using C = DqCfg<D>;
+  using T = Tile<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  if (smem_base & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, 0x20000 | kBSiteAlign);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_base + C::kOffBar + 8u * i; };
+
+  const int ntiles = (N + 127) >> 7;
+  const int qt = ntiles - 1 - static_cast<int>(blockIdx.x);  // heaviest Q tile first
+  const int bh = blockIdx.y;
+  const int nkv = qt + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(C::kBarQ), 1);
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(bar(C::kBarKFull + i), 1);
+      mbar_init(bar(C::kBarKEmpty + i), 1);
+      mbar_init(bar(C::kBarVFull + i), 1);
+      mbar_init(bar(C::kBarVEmpty + i), 1);
+    }
+    mbar_init(bar(C::kBarSFull), 1);
+    mbar_init(bar(C::kBarDpFull), 1);
+    mbar_init(bar(C::kBarDsReady), 256);
+    mbar_init(bar(C::kBarDone), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == C::kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtx w{abort_flag, status};
+
+  if (warp >= C::kMmaWarp) {
+    if (warp == C::kLoadWarp && lane == 0) {
+      prefetch_tensormap(&tq);
+      prefetch_tensormap(&tk);
+      prefetch_tensormap(&tv);
+      prefetch_tensormap(&tdo);
+      mbar_arrive_expect_tx(bar(C::kBarQ), 2 * T::kTileBytes + 1024);
+      for (int ch = 0; ch < T::kChunks; ++ch) {
+        tma_load_3d(smem_base + C::kOffQ + ch * T::kChunkTileBytes, &tq, ch * T::kChunkElems,
+                    qt * 128, bh, bar(C::kBarQ));
+        tma_load_3d(smem_base + C::kOffDO + ch * T::kChunkTileBytes, &tdo, ch * T::kChunkElems,
+                    qt * 128, bh, bar(C::kBarQ));
+      }
+      bulk_load_1d(smem_base + C::kOffStats,
+                   rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024, bar(C::kBarQ));
+      for (int j = 0; j < nkv; ++j) {
+        const int s = j % C::kStages, ph = (j / C::kStages) & 1;
+        if (!mbar_wait(bar(C::kBarKEmpty + s), ph ^ 1, w, kBSiteLoadQ)) break;
+        mbar_arrive_expect_tx(bar(C::kBarKFull + s), T::kTileBytes);
+        for (int ch = 0; ch < T::kChunks; ++ch)
+          tma_load_3d(smem_base + C::kOffK + s * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
+                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + s));
+        if (!mbar_wait(bar(C::kBarVEmpty + s), ph ^ 1, w, kBSiteLoadDO)) break;
+        mbar_arrive_expect_tx(bar(C::kBarVFull + s), T::kTileBytes);
+        for (int ch = 0; ch < T::kChunks; ++ch)
+          tma_load_3d(smem_base + C::kOffV + s * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
+                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarVFull + s));
+      }
+    } else if (warp == C::kMmaWarp && lane == 0) {
+      constexpr uint32_t idesc_t = make_idesc(128, 128, BF16, false, false);  // S, dP
+      constexpr uint32_t idesc_dq = make_idesc(128, D, BF16, false, true);    // dQ
+      const uint32_t qa = smem_base + C::kOffQ, doa = smem_base + C::kOffDO;
+      auto issue_t = [&](uint32_t col, uint32_t a_base, uint32_t b_base) {
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint32_t off =
+              (k / T::kKStepsPerChunk) * T::kChunkTileBytes + (k % T::kKStepsPerChunk) * 32;
+          mma_ss(tmem_base + col, make_smem_desc(a_base + off, 16, T::kAtomBytes, T::kSwizzleMode),
+                 make_smem_desc(b_base + off, 16, T::kAtomBytes, T::kSwizzleMode), idesc_t, k > 0);
+        }
+      };
+      bool ok = mbar_wait(bar(C::kBarQ), 0, w, kBSiteMmaQ);
+      for (int j = 0; ok && j <= nkv; ++j) {
+        // issue S(j), dP(j) (if any), then dQ += dS(j-1) K_{j-1}
+        if (j < nkv) {
+          const int s = j % C::kStages, ph = (j / C::kStages) & 1;
+          if (j > 0) {
+            // S and dP regions are rewritten: dS(j-1) must have been produced from them, and
+            // the dQ MMA that reads dS(j-1) is issued first (in-order pipe).
+            if (!(ok = mbar_wait(bar(C::kBarDsReady), (j - 1) & 1, w, kBSiteMmaDs))) break;
+            tc_fence_after();
+            const int sp = (j - 1) % C::kStages;
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              mma_ts(tmem_base + C::kColDQ, tmem_base + C::kColDp + packed_col(k),
+                     make_smem_desc(smem_base + C::kOffK + sp * T::kTileBytes + k * 2 * T::kAtomBytes,
+                                    T::kChunkTileBytes, T::kAtomBytes, T::kSwizzleMode),
+                     idesc_dq, (j > 1 || k > 0) ? 1u : 0u);
+            mma_commit(bar(C::kBarKEmpty + sp));
+          }
+          if (!(ok = mbar_wait(bar(C::kBarKFull + s), ph, w, kBSiteMmaKV))) break;
+          issue_t(C::kColS, qa, smem_base + C::kOffK + s * T::kTileBytes);
+          mma_commit(bar(C::kBarSFull));
+          if (!(ok = mbar_wait(bar(C::kBarVFull + s), ph, w, kBSiteMmaDO))) break;
+          issue_t(C::kColDp, doa, smem_base + C::kOffV + s * T::kTileBytes);
+          mma_commit(bar(C::kBarDpFull));
+          mma_commit(bar(C::kBarVEmpty + s));
+        } else {
+          if (!(ok = mbar_wait(bar(C::kBarDsReady), (j - 1) & 1, w, kBSiteMmaDs))) break;
+          tc_fence_after();
+          const int sp = (j - 1) % C::kStages;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            mma_ts(tmem_base + C::kColDQ, tmem_base + C::kColDp + packed_col(k),
+                   make_smem_desc(smem_base + C::kOffK + sp * T::kTileBytes + k * 2 * T::kAtomBytes,
+                                  T::kChunkTileBytes, T::kAtomBytes, T::kSwizzleMode),
+                   idesc_dq, (j > 1 || k > 0) ? 1u : 0u);
+          mma_commit(bar(C::kBarDone));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    const int wg = warp >> 2;
+    const int w4 = warp & 3;
+    const int r = w4 * 32 + lane;  // q row in the tile = tensor-memory lane
+    const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
+    const uint32_t tS = tmem_base + lane_base + C::kColS + wg * 64;
+    const uint32_t tDp = tmem_base + lane_base + C::kColDp + wg * 64;
+    bool ok = mbar_wait_warp(bar(C::kBarQ), 0, w, kBSiteCmpQ);
+    float lse2 = 0.f, dlt = 0.f;
+    if (ok) {
+      const float* stats = reinterpret_cast<const float*>(smem + C::kOffStats);
+      lse2 = stats[r];
+      dlt = stats[128 + r];
+    }
+    for (int j = 0; ok && j < nkv; ++j) {
+      if (!(ok = mbar_wait_warp(bar(C::kBarSFull), j & 1, w, kBSiteCmpSt))) break;
+      tc_fence_after();
+      float p[64];
+      {
+        uint32_t sr[64];
+        tmem_ld_x32(tS, sr);
+        tmem_ld_x32(tS + 32, sr + 32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 64; ++c) p[c] = ex2(fmaf(__uint_as_float(sr[c]), scale_log2, -lse2));
+      }
+      if (j == qt) {  // diagonal tile: keep kv <= q
+#pragma unroll
+        for (int c = 0; c < 64; ++c) p[c] = (wg * 64 + c <= r) ? p[c] : 0.f;
+      }
+      if (!(ok = mbar_wait_warp(bar(C::kBarDpFull), j & 1, w, kBSiteCmpDpt))) break;
+      tc_fence_after();
+      uint32_t dsk[32];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t dp[32];
+        tmem_ld_x32(tDp + 32 * h, dp);
+        tmem_wait_ld();
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+          const float d0 = p[32 * h + 2 * c] * (__uint_as_float(dp[2 * c]) - dlt) * scale;
+          const float d1 = p[32 * h + 2 * c + 1] * (__uint_as_float(dp[2 * c + 1]) - dlt) * scale;
+          dsk[16 * h + c] = pack2<BF16>(d0, d1);
+        }
+      }
+      tmem_st_x32(tDp, dsk);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(C::kBarDsReady));
+    }
+    if (ok && wg == 0 && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
+      tc_fence_after();
+      store_rows_16bit<D, BF16>(tmem_base + lane_base + C::kColDQ, smem + C::kOffDO, w4, lane, &tdq,
+                                qt * 128, bh, N);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == C::kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int D, bool BF16, bool FUSE>
+cudaError_t launch_dkdv_t(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                          const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdk,
+                          const CUtensorMap& tdv, const float* rowstats, float* dq_accum,
+                          int* status, cudaStream_t stream) {
+  using C = DkdvCfg<D, FUSE>;
+  auto kern = bwd_dkdv_kernel<D, BF16, FUSE>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int ntiles = (s.N + 127) / 128;
+  dim3 grid(ntiles, s.B * s.H);
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum,
+                                                     s.N, s.scale, s.scale * 1.4426950408889634f,
+                                                     status);
+  return cudaGetLastError();
+}
+
+template <int D, bool BF16>
+cudaError_t launch_dq_t(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                        const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq,
+                        const float* rowstats, int* status, cudaStream_t stream) {
+  using C = DqCfg<D>;
+  auto kern = bwd_dq_kernel<D, BF16>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  const int ntiles = (s.N + 127) / 128;
+  dim3 grid(ntiles, s.B * s.H);
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, rowstats, s.N, s.scale,
+                                                     s.scale * 1.4426950408889634f, status);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                            const CUtensorMap& tv, const CUtensorMap& tdo,
+                            const CUtensorMap& tdk, const CUtensorMap& tdv,
+                            const float* rowstats, float* dq_accum, int fuse_dq, int* status,
+                            cudaStream_t stream) {
+#define FA2_ARGS s, tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum, status, stream
+#define FA2_CASE(DD)                                                                        \
+  case DD:                                                                                  \
+    if (fuse_dq)                                                                            \
+      return s.dtype ? launch_dkdv_t<DD, true, true>(FA2_ARGS)                              \
+                     : launch_dkdv_t<DD, false, true>(FA2_ARGS);                            \
+    return s.dtype ? launch_dkdv_t<DD, true, false>(FA2_ARGS)                               \
+                   : launch_dkdv_t<DD, false, false>(FA2_ARGS);
+  switch (s.D) {
+    FA2_CASE(32)
+    FA2_CASE(64)
+    FA2_CASE(128)
+  }
+#undef FA2_CASE
+#undef FA2_ARGS
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_bwd_dq(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                          const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq,
+                          const float* rowstats, int* status, cudaStream_t stream) {
+#define FA2_ARGS s, tq, tk, tv, tdo, tdq, rowstats, status, stream
+#define FA2_CASE(DD)                                                   \
+  case DD:                                                             \
+    return s.dtype ? launch_dq_t<DD, true>(FA2_ARGS)                   \
+                   : launch_dq_t<DD, false>(FA2_ARGS);
+  switch (s.D) {
+    FA2_CASE(32)
+    FA2_CASE(64)
+    FA2_CASE(128)
+  }
+#undef FA2_CASE
+#undef FA2_ARGS
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fa2

@@ -1,0 +1,233 @@
+// C ABI of the library (declared in include/fa2_b200.h): argument validation, tensor-map
+// construction and kernel dispatch.  Nothing here allocates device memory or synchronises,
+// except fa2_device_status which reads the status word back.
+#include <cmath>
+#include <cstdint>
+#include <mutex>
+
+#include "../../include/fa2_b200.h"
+#include "common.cuh"
+
+namespace fa2 {
+
+// One status word per device: kernels write here when a bounded wait expires.
+__device__ int g_status_word;
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+EncodeTiledFn get_encode() {
+  std::call_once(g_encode_once, [] {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  });
+  return g_encode;
+}
+
+struct DeviceState {
+  std::once_flag once;
+  int cc_major = 0;
+  int* status = nullptr;
+  cudaError_t err = cudaSuccess;
+};
+DeviceState g_dev[kMaxDevices];
+
+// Per-device set-up on first use: compute capability and the address of the status word.
+int device_state(DeviceState** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return FA2_ERR_ARCH;
+  DeviceState& d = g_dev[dev];
+  std::call_once(d.once, [&] {
+    d.err = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (d.err == cudaSuccess)
+      d.err = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_status_word);
+  });
+  if (d.err != cudaSuccess) return static_cast<int>(d.err);
+  if (d.cc_major != 10) return FA2_ERR_ARCH;
+  *out = &d;
+  return FA2_OK;
+}
+
+// Tensor map over a dense [BH, N, D] 16-bit tensor with box (chunk, box_rows, 1).
+int make_map(CUtensorMap* m, const void* base, int dtype, int D, int N, long long BH,
+             int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return FA2_ERR_DRIVER;
+  const int chunk = D >= 64 ? 64 : 32;
+  const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(N),
+                              static_cast<cuuint64_t>(BH)};
+  const cuuint64_t gstride[2] = {static_cast<cuuint64_t>(D) * 2,
+                                 static_cast<cuuint64_t>(N) * D * 2};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(chunk), static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUresult r =
+      enc(m, dtype ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+          const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+          chunk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FA2_OK : FA2_ERR_DRIVER;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_shape(int B, int H, int N, int D, int dtype) {
+  if (D != 32 && D != 64 && D != 128) return FA2_ERR_HEAD_DIM;
+  if (dtype != FA2_DTYPE_FP16 && dtype != FA2_DTYPE_BF16) return FA2_ERR_DTYPE;
+  if (B <= 0 || H <= 0 || N <= 0) return FA2_ERR_SHAPE;
+  if (static_cast<long long>(B) * H > 65535) return FA2_ERR_SHAPE;
+  if (N > (1 << 24)) return FA2_ERR_SHAPE;
+  return FA2_OK;
+}
+
+}  // namespace
+}  // namespace fa2
+
+using namespace fa2;
+
+extern "C" {
+
+int fa2_abi_version(void) { return FA2_ABI_VERSION; }
+
+const char* fa2_strerror(int code) {
+  switch (code) {
+    case FA2_OK: return "success";
+    case FA2_ERR_NULL_POINTER: return "a required pointer is NULL";
+    case FA2_ERR_HEAD_DIM: return "head dimension must be 32, 64 or 128";
+    case FA2_ERR_DTYPE: return "dtype must be 0 (fp16) or 1 (bf16)";
+    case FA2_ERR_MISALIGNED: return "tensor pointers must be 16-byte aligned";
+    case FA2_ERR_SHAPE: return "B, H, N must be positive, B*H <= 65535, N <= 2^24";
+    case FA2_ERR_ARCH: return "the current device is not compute capability 10.x (B200)";
+    case FA2_ERR_DEVICE_STATUS: return "a kernel abandoned a bounded wait (see fa2_device_status)";
+    case FA2_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
+    case FA2_ERR_SCALE: return "softmax scale must be finite and > 0";
+    case FA2_ERR_WORKSPACE: return "dq_accum workspace is required when deterministic == 0";
+    default: break;
+  }
+  if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+  return "unknown fa2 error code";
+}
+
+int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int N,
+            int D, int dtype, float scale, fa2_stream_t stream) {
+  if (!q || !k || !v || !o || !lse) return FA2_ERR_NULL_POINTER;
+  if (int e = check_shape(B, H, N, D, dtype)) return e;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return FA2_ERR_MISALIGNED;
+  if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
+  DeviceState* d = nullptr;
+  if (int e = device_state(&d)) return e;
+  const long long BH = static_cast<long long>(B) * H;
+  CUtensorMap tq, tk, tv, to;
+  if (int e = make_map(&tq, q, dtype, D, N, BH, 128)) return e;
+  if (int e = make_map(&tk, k, dtype, D, N, BH, 128)) return e;
+  if (int e = make_map(&tv, v, dtype, D, N, BH, 128)) return e;
+  if (int e = make_map(&to, o, dtype, D, N, BH, 32)) return e;
+  const AttnShape s{B, H, N, D, dtype, scale};
+  return static_cast<int>(
+      launch_fwd(s, tq, tk, tv, to, lse, d->status, static_cast<cudaStream_t>(stream)));
+}
+
+size_t fa2_rowstats_bytes(int B, int H, int N) {
+  if (B <= 0 || H <= 0 || N <= 0) return 0;
+  const size_t ntiles = (static_cast<size_t>(N) + 127) / 128;
+  return static_cast<size_t>(B) * H * ntiles * 256 * sizeof(float);
+}
+
+int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float* rowstats, int B,
+                       int H, int N, int D, int dtype, fa2_stream_t stream) {
+  if (!o || !dout || !lse || !rowstats) return FA2_ERR_NULL_POINTER;
+  if (int e = check_shape(B, H, N, D, dtype)) return e;
+  if (!aligned16(o) || !aligned16(dout) || !aligned16(rowstats)) return FA2_ERR_MISALIGNED;
+  DeviceState* d = nullptr;
+  if (int e = device_state(&d)) return e;
+  const AttnShape s{B, H, N, D, dtype, 1.f};
+  return static_cast<int>(
+      launch_bwd_preprocess(s, o, dout, lse, rowstats, static_cast<cudaStream_t>(stream)));
+}
+
+size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
+  if (deterministic || B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
+  const size_t ntiles = (static_cast<size_t>(N) + 127) / 128;
+  return static_cast<size_t>(B) * H * ntiles * 128 * D * sizeof(float);
+}
+
+int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const float* rowstats,
+            void* dq, void* dk, void* dv, float* dq_accum, int B, int H, int N, int D, int dtype,
+            float scale, int deterministic, fa2_stream_t stream) {
+  if (!q || !k || !v || !dout || !rowstats || !dq || !dk || !dv) return FA2_ERR_NULL_POINTER;
+  if (int e = check_shape(B, H, N, D, dtype)) return e;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(dout) || !aligned16(dq) ||
+      !aligned16(dk) || !aligned16(dv) || !aligned16(rowstats))
+    return FA2_ERR_MISALIGNED;
+  if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
+  if (!deterministic && !dq_accum) return FA2_ERR_WORKSPACE;
+  if (!deterministic && !aligned16(dq_accum)) return FA2_ERR_MISALIGNED;
+  DeviceState* d = nullptr;
+  if (int e = device_state(&d)) return e;
+  const long long BH = static_cast<long long>(B) * H;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
+  if (int e = make_map(&tq, q, dtype, D, N, BH, 128)) return e;
+  if (int e = make_map(&tk, k, dtype, D, N, BH, 128)) return e;
+  if (int e = make_map(&tv, v, dtype, D, N, BH, 128)) return e;
+  if (int e = make_map(&tdo, dout, dtype, D, N, BH, 128)) return e;
+  if (int e = make_map(&tdk, dk, dtype, D, N, BH, 32)) return e;
+  if (int e = make_map(&tdv, dv, dtype, D, N, BH, 32)) return e;
+  const AttnShape s{B, H, N, D, dtype, scale};
+  if (deterministic) {
+    if (int e = make_map(&tdq, dq, dtype, D, N, BH, 32)) return e;
+    cudaError_t ce =
+        launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, nullptr, 0, d->status, st);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+    return static_cast<int>(launch_bwd_dq(s, tq, tk, tv, tdo, tdq, rowstats, d->status, st));
+  }
+  cudaError_t ce = cudaMemsetAsync(dq_accum, 0, fa2_bwd_workspace_bytes(B, H, N, D, 0), st);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  ce = launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum, 1, d->status, st);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  return static_cast<int>(launch_dq_convert(s, dq_accum, dq, st));
+}
+
+int fa2_device_status(int* status_out) {
+  if (!status_out) return FA2_ERR_NULL_POINTER;
+  DeviceState* d = nullptr;
+  if (int e = device_state(&d)) return e;
+  cudaError_t ce = cudaDeviceSynchronize();
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  ce = cudaMemcpy(status_out, d->status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  if (*status_out != 0) ce = cudaMemset(d->status, 0, sizeof(int));
+  return static_cast<int>(ce);
+}
+
+int fa2_selftest_mma(int form, const void* a, const void* b, float* c, int D, int dtype,
+                     fa2_stream_t stream) {
+  if (!a || !b || !c) return FA2_ERR_NULL_POINTER;
+  if (form < 0 || form > 2) return FA2_ERR_SHAPE;
+  if (int e = check_shape(1, 1, 128, D, dtype)) return e;
+  if (!aligned16(a) || !aligned16(b)) return FA2_ERR_MISALIGNED;
+  DeviceState* d = nullptr;
+  if (int e = device_state(&d)) return e;
+  CUtensorMap ta, tb;
+  // form 0 reads A [128, D] through TMA; forms 1 and 2 read A [128, 128] with plain loads.
+  if (int e = make_map(&ta, form == 0 ? a : b, dtype, D, 128, 1, 128)) return e;
+  if (int e = make_map(&tb, b, dtype, D, 128, 1, 128)) return e;
+  return static_cast<int>(launch_selftest_mma(form, ta, tb, a, c, D, dtype, d->status,
+                                              static_cast<cudaStream_t>(stream)));
+}
+
+}  // extern "C"

@@ -1,0 +1,84 @@
+// Tile geometry shared by the attention kernels, and the host-side launcher interface
+// between the translation units of the library.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace fa2 {
+
+// A 128-row tile of a [.., N, D] tensor is staged in shared memory as D/CH "chunk tiles" of
+// [128 rows][CH elements]; CH*2 bytes is the swizzle span (128 B for D >= 64, 64 B for D = 32).
+// This is exactly what one TMA box of (CH, 128, 1) with the matching swizzle mode produces,
+// and what the tensor-core shared-memory descriptors below describe.
+template <int D>
+struct Tile {
+  static_assert(D == 32 || D == 64 || D == 128, "head dim must be 32, 64 or 128");
+  static constexpr int kRows = 128;
+  static constexpr int kChunkElems = D >= 64 ? 64 : 32;
+  static constexpr int kChunks = D / kChunkElems;
+  static constexpr int kRowBytes = kChunkElems * 2;             // 128 or 64
+  static constexpr int kChunkTileBytes = kRows * kRowBytes;     // 16384 or 8192
+  static constexpr int kTileBytes = kChunks * kChunkTileBytes;  // 128 * D * 2
+  static constexpr int kAtomBytes = 8 * kRowBytes;              // 8-row swizzle atom
+  static constexpr uint32_t kSwizzleMode = kRowBytes == 128 ? 2u : 4u;
+  static constexpr uint32_t kSwizzleMask = kRowBytes == 128 ? 7u : 3u;
+  static constexpr int kKStepsPerChunk = kChunkElems / 16;  // MMAs (K = 16) per chunk tile
+};
+
+// Byte offset of the 16-byte piece `piece` of row `row` inside one chunk tile, after the
+// hardware XOR swizzle (address bits [4,7) ^= bits [7,10), restricted to the swizzle span).
+template <int D>
+__host__ __device__ __forceinline__ uint32_t swizzled_offset(uint32_t row, uint32_t piece) {
+  const uint32_t off = row * Tile<D>::kRowBytes + piece * 16u;
+  return off ^ (((off >> 7) & Tile<D>::kSwizzleMask) << 4);
+}
+
+// Same for a [128 rows][64 elements] 16-bit tile with 128-byte rows, whatever D is (used
+// for the score-gradient tile, whose row length is the tile width 128, not D).
+__host__ __device__ __forceinline__ uint32_t swizzled_offset_128B(uint32_t row, uint32_t piece) {
+  const uint32_t off = row * 128u + piece * 16u;
+  return off ^ (((off >> 7) & 7u) << 4);
+}
+
+// ----------------------------------------------------------------------------------------
+// Host launchers (one per kernel family), defined in the .cu files of this directory.
+// Tensor maps describe [B*H, N, D] views: q/k/v/dout/o... with box (CH, 128, 1).
+// ----------------------------------------------------------------------------------------
+struct AttnShape {
+  int B, H, N, D;
+  int dtype;  // 0 = fp16, 1 = bf16
+  float scale;
+};
+
+cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                       const CUtensorMap& tv, const CUtensorMap& to, float* lse, int* status,
+                       cudaStream_t stream);
+
+// rowstats[bh][t][0][r] = lse * log2(e) (+inf for padded rows), rowstats[bh][t][1][r] = delta.
+cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const void* dout,
+                                  const float* lse, float* rowstats, cudaStream_t stream);
+
+// dK/dV per KV tile.  fuse_dq != 0 also accumulates dQ into dq_accum with fp32 atomic adds.
+// dq_accum layout: [bh][t][w = 4][k = D/4][lane = 32][4] floats, holding element
+// (row 128*t + 32*w + lane, col 4*k + 0..3).
+cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                            const CUtensorMap& tv, const CUtensorMap& tdo,
+                            const CUtensorMap& tdk, const CUtensorMap& tdv,
+                            const float* rowstats, float* dq_accum, int fuse_dq, int* status,
+                            cudaStream_t stream);
+
+// dQ per Q tile, ascending KV order (deterministic path).
+cudaError_t launch_bwd_dq(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                          const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq,
+                          const float* rowstats, int* status, cudaStream_t stream);
+
+// dq = convert(dq_accum) (non-deterministic path).
+cudaError_t launch_dq_convert(const AttnShape& s, const float* dq_accum, void* dq,
+                              cudaStream_t stream);
+
+cudaError_t launch_selftest_mma(int form, const CUtensorMap& ta, const CUtensorMap& tb,
+                                const void* a_raw, float* c, int D, int dtype, int* status,
+                                cudaStream_t stream);
+
+}  // namespace fa2

@@ -1,0 +1,184 @@
+// Bandwidth-bound helpers of the backward pass.
+//
+//   bwd_preprocess_kernel  delta[row] = sum_d float(o[row,d]) * float(dout[row,d])
+//       replaces _backward_preprocess_do_o_dot (_triton_kernels_v2.py:532-608 of the
+//       reference).  Algorithmic traffic per row: 2 * D * 2 bytes read + 4 bytes written.
+//   dq_convert_kernel      dq = 16-bit(dq_accum), the single fp32 -> 16-bit rounding the
+//       reference performs with dq.copy_(dq_accum) (flash_attention_2.py:277).
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace fa2 {
+namespace {
+
+template <bool BF16>
+__device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w};
+  const uint32_t bw[4] = {b.x, b.y, b.z, b.w};
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 fa, fb;
+    if constexpr (BF16) {
+      fa = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&aw[i]));
+      fb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&bw[i]));
+    } else {
+      fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+      fb = __half22float2(*reinterpret_cast<const __half2*>(&bw[i]));
+    }
+    acc = fmaf(fa.x, fb.x, acc);
+    acc = fmaf(fa.y, fb.y, acc);
+  }
+  return acc;
+}
+
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+constexpr int kPreThreads = 256;
+constexpr int kPreRowsInFlight = 2;  // independent rows per thread group, for loads in flight
+constexpr float kLog2e = 1.4426950408889634f;
+
+// A group of D/8 adjacent lanes owns one row: each lane reads one 16-byte piece of o and of
+// dout, multiplies, and the group reduces with shuffles in a fixed order (deterministic).
+// Rows are enumerated over the padded range [BH][T*128] so that the padding of rowstats is
+// written too (lse2 = +inf makes every probability of a padded row exactly 0 downstream).
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kPreThreads)
+    bwd_preprocess_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dout,
+                          const float* __restrict__ lse, float* __restrict__ rowstats, int N,
+                          int npad, long long padded_rows) {
+  constexpr int kLanesPerRow = D / 8;
+  constexpr int kRowsPerBlockPass = kPreThreads / kLanesPerRow;
+  const int sub = threadIdx.x % kLanesPerRow;
+  const long long row_in_pass = threadIdx.x / kLanesPerRow;
+  const long long base_row =
+      static_cast<long long>(blockIdx.x) * (kRowsPerBlockPass * kPreRowsInFlight) + row_in_pass;
+  uint4 a[kPreRowsInFlight], b[kPreRowsInFlight];
+  long long src_row[kPreRowsInFlight];
+#pragma unroll
+  for (int i = 0; i < kPreRowsInFlight; ++i) {
+    const long long prow = base_row + static_cast<long long>(i) * kRowsPerBlockPass;
+    const long long bh = prow / npad;
+    const int rr = static_cast<int>(prow - bh * npad);
+    src_row[i] = (prow < padded_rows && rr < N) ? bh * N + rr : -1;
+    if (src_row[i] >= 0) {
+      a[i] = ld_stream(o + src_row[i] * kLanesPerRow + sub);
+      b[i] = ld_stream(dout + src_row[i] * kLanesPerRow + sub);
+    } else {
+      a[i] = make_uint4(0, 0, 0, 0);
+      b[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kPreRowsInFlight; ++i) {
+    float acc = dot8<BF16>(a[i], b[i]);
+#pragma unroll
+    for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
+      acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    const long long prow = base_row + static_cast<long long>(i) * kRowsPerBlockPass;
+    if (sub == 0 && prow < padded_rows) {
+      // prow = (bh*T + t)*128 + r  ->  rowstats[(bh*T + t)*256 + {0,128} + r]
+      const long long tile = prow >> 7;
+      const int r = static_cast<int>(prow & 127);
+      const bool valid = src_row[i] >= 0;
+      rowstats[tile * 256 + r] = valid ? lse[src_row[i]] * kLog2e : INFINITY;
+      rowstats[tile * 256 + 128 + r] = valid ? acc : 0.f;
+    }
+  }
+}
+
+// One thread converts 8 consecutive head-dim elements of one row.  Consecutive lanes take
+// consecutive rows of the same 32-row group, so the fp32 reads are contiguous 512-byte runs
+// (the layout the fused backward kernel accumulates into).
+template <int D, bool BF16>
+__global__ void __launch_bounds__(256)
+    dq_convert_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, int N, int ntiles,
+                      long long total) {
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  // idx = ((tile_global * 4 + w) * (D/8) + k8) * 32 + lane
+  const int lane = static_cast<int>(idx & 31);
+  long long t = idx >> 5;
+  const int k8 = static_cast<int>(t % (D / 8));
+  t /= (D / 8);
+  const int w = static_cast<int>(t & 3);
+  const long long tile_global = t >> 2;
+  const long long bh = tile_global / ntiles;
+  const int tile = static_cast<int>(tile_global - bh * ntiles);
+  const int row = tile * 128 + w * 32 + lane;
+  if (row >= N) return;
+  const long long blk = (tile_global * 4 + w) * (D / 4);  // in units of [32 lanes][float4]
+  const float4 x = acc[(blk + 2 * k8) * 32 + lane];
+  const float4 y = acc[(blk + 2 * k8 + 1) * 32 + lane];
+  uint4 r;
+  r.x = pack2<BF16>(x.x, x.y);
+  r.y = pack2<BF16>(x.z, x.w);
+  r.z = pack2<BF16>(y.x, y.y);
+  r.w = pack2<BF16>(y.z, y.w);
+  dq[(bh * N + row) * (D / 8) + k8] = r;
+}
+
+template <int D, bool BF16>
+cudaError_t launch_pre_t(const AttnShape& s, const void* o, const void* dout, const float* lse,
+                         float* rowstats, cudaStream_t stream) {
+  const int ntiles = (s.N + 127) / 128;
+  const int npad = ntiles * 128;
+  const long long padded_rows = static_cast<long long>(s.B) * s.H * npad;
+  constexpr int kRowsPerBlock = kPreThreads / (D / 8) * kPreRowsInFlight;
+  const long long blocks = (padded_rows + kRowsPerBlock - 1) / kRowsPerBlock;
+  bwd_preprocess_kernel<D, BF16><<<static_cast<unsigned>(blocks), kPreThreads, 0, stream>>>(
+      static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, s.N, npad,
+      padded_rows);
+  return cudaGetLastError();
+}
+
+template <int D, bool BF16>
+cudaError_t launch_cvt_t(const AttnShape& s, const float* dq_accum, void* dq,
+                         cudaStream_t stream) {
+  const int ntiles = (s.N + 127) / 128;
+  const long long total = static_cast<long long>(s.B) * s.H * ntiles * 128 * (D / 8);
+  const long long blocks = (total + 255) / 256;
+  dq_convert_kernel<D, BF16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+      reinterpret_cast<const float4*>(dq_accum), static_cast<uint4*>(dq), s.N, ntiles, total);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const void* dout,
+                                  const float* lse, float* rowstats, cudaStream_t stream) {
+#define FA2_CASE(DD)                                                                 \
+  case DD:                                                                           \
+    return s.dtype ? launch_pre_t<DD, true>(s, o, dout, lse, rowstats, stream)       \
+                   : launch_pre_t<DD, false>(s, o, dout, lse, rowstats, stream);
+  switch (s.D) {
+    FA2_CASE(32)
+    FA2_CASE(64)
+    FA2_CASE(128)
+  }
+#undef FA2_CASE
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_dq_convert(const AttnShape& s, const float* dq_accum, void* dq,
+                              cudaStream_t stream) {
+#define FA2_CASE(DD)                                                        \
+  case DD:                                                                  \
+    return s.dtype ? launch_cvt_t<DD, true>(s, dq_accum, dq, stream)        \
+                   : launch_cvt_t<DD, false>(s, dq_accum, dq, stream);
+  switch (s.D) {
+    FA2_CASE(32)
+    FA2_CASE(64)
+    FA2_CASE(128)
+  }
+#undef FA2_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace fa2

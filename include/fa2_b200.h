@@ -1,0 +1,129 @@
+/*
+ * fa2_b200.h — C ABI of the B200 (sm_100a) causal FlashAttention-2 library.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, launches on the
+ * stream it is given and returns without synchronising (the one exception,
+ * fa2_device_status, says so).  The caller owns every buffer.  All tensors are dense
+ * row-major [B, H, N, D] (strides implied) on the current CUDA device; lse is dense fp32
+ * [B, H, N].  D must be 32, 64 or 128; dtype 0 = fp16, 1 = bf16.
+ *
+ * Return value: 0 = success; negative = argument / environment error (table below);
+ * positive = a cudaError_t from a launch or attribute call.
+ *
+ * The functions below replace these pieces of flash-attention-triton (paths inside that
+ * project):
+ *   fa2_fwd             src/flash_attention_triton/flash_attention_2.py:61-144
+ *                       (_flash_attention_forward) + _triton_kernels_v2.py:11-189
+ *   fa2_bwd_preprocess  _triton_kernels_v2.py:532-608 (_backward_preprocess_do_o_dot),
+ *                       launched from flash_attention_2.py:218-234
+ *   fa2_bwd             flash_attention_2.py:147-277 (_flash_attention_backward) +
+ *                       _triton_kernels_v2.py:192-529; `deterministic` mirrors
+ *                       SEQUENCE_PARALLEL=False of the reference's config tables
+ *                       (flash_attention_2.py:570-589)
+ */
+#ifndef FA2_B200_H_
+#define FA2_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA2_ABI_VERSION 1
+
+#define FA2_DTYPE_FP16 0
+#define FA2_DTYPE_BF16 1
+
+#define FA2_OK 0
+#define FA2_ERR_NULL_POINTER (-1)      /* a required pointer is NULL */
+#define FA2_ERR_HEAD_DIM (-2)          /* D not in {32, 64, 128} */
+#define FA2_ERR_DTYPE (-3)             /* dtype not FA2_DTYPE_FP16 / FA2_DTYPE_BF16 */
+#define FA2_ERR_MISALIGNED (-4)        /* a tensor pointer is not 16-byte aligned */
+#define FA2_ERR_SHAPE (-5)             /* B, H or N <= 0, or B*H > 65535, or N too large */
+#define FA2_ERR_ARCH (-6)              /* current device is not compute capability 10.x */
+#define FA2_ERR_DEVICE_STATUS (-7)     /* a kernel gave up on a bounded wait */
+#define FA2_ERR_DRIVER (-8)            /* cuTensorMapEncodeTiled unavailable or failed */
+#define FA2_ERR_SCALE (-9)             /* softmax scale not finite or not > 0 */
+#define FA2_ERR_WORKSPACE (-10)        /* dq_accum is NULL although deterministic == 0 */
+
+/* Opaque stream handle: pass a cudaStream_t (NULL = legacy default stream). */
+typedef void* fa2_stream_t;
+
+int fa2_abi_version(void);
+
+/* Static, human-readable text for a return code of this library. */
+const char* fa2_strerror(int code);
+
+/*
+ * Forward: O = softmax_causal(scale * Q K^T) V, lse[b,h,i] = log sum_j exp(scale * s_ij)
+ * (natural log).  Replaces _flash_attention_forward / _forward_kernel; unlike the
+ * reference (flash_attention_2.py:98-100) lse is not padded and no scratch buffer is used.
+ */
+int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
+            int B, int H, int N, int D, int dtype, float scale, fa2_stream_t stream);
+
+/*
+ * Backward preprocess.  Computes delta[b,h,i] = sum_d float(o[b,h,i,d]) * float(dout[b,h,i,d])
+ * (replaces _backward_preprocess_do_o_dot) and stores it, together with lse * log2(e), in the
+ * tile-blocked fp32 array `rowstats` that fa2_bwd consumes:
+ *     rowstats[(b*H + h)][t][0][r] = lse[b,h,128*t + r] * log2(e)   (+inf for rows >= N)
+ *     rowstats[(b*H + h)][t][1][r] = delta[b,h,128*t + r]           (0    for rows >= N)
+ * with t in [0, ceil(N/128)), r in [0, 128).  One 1 KiB bulk copy then stages both vectors of
+ * a Q tile; the padding plays the role of the reference's seqlen_q_rounded buffers
+ * (flash_attention_2.py:98-100,180).  rowstats must hold fa2_rowstats_bytes() bytes and be
+ * 16-byte aligned.
+ */
+int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float* rowstats,
+                       int B, int H, int N, int D, int dtype, fa2_stream_t stream);
+
+size_t fa2_rowstats_bytes(int B, int H, int N);
+
+/*
+ * Backward main.  Inputs q,k,v,dout and rowstats (from fa2_bwd_preprocess); outputs
+ * dq,dk,dv in the input dtype.
+ *   deterministic != 0: dK/dV kernel + a separate dQ kernel; every output tile has one
+ *     owner and a fixed accumulation order, so results are bit-identical across runs,
+ *     SM counts and (batch, head) partitionings.  dq_accum is not used (may be NULL).
+ *   deterministic == 0: one fused kernel per KV tile adds its dQ contributions into the
+ *     fp32 workspace dq_accum with atomic adds (the reference's SEQUENCE_PARALLEL mode,
+ *     _triton_kernels_v2.py:337-339), then a convert pass writes dq, rounding once like
+ *     dq.copy_(dq_accum) (flash_attention_2.py:277).  dq_accum must hold
+ *     fa2_bwd_workspace_bytes() bytes, 16-byte aligned; this call zeroes it itself.  Its
+ *     layout is private (tile-blocked so that every warp-wide atomic is one contiguous
+ *     512-byte run).
+ */
+int fa2_bwd(const void* q, const void* k, const void* v, const void* dout,
+            const float* rowstats,
+            void* dq, void* dk, void* dv, float* dq_accum,
+            int B, int H, int N, int D, int dtype, float scale, int deterministic,
+            fa2_stream_t stream);
+
+/* Bytes of fp32 workspace fa2_bwd needs (0 when deterministic != 0). */
+size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic);
+
+/*
+ * Reads and clears the per-device status word that kernels set when a bounded wait
+ * expires (they then drain and return instead of hanging).  Synchronises the device.
+ * *status_out = 0 when every kernel since the last call ran to completion.
+ * No counterpart in the reference (Triton kernels have no such protocol).
+ */
+int fa2_device_status(int* status_out);
+
+/*
+ * Diagnostics: runs one tensor-core tile product through a single operand form used by the
+ * attention kernels and writes the fp32 result, so that a driver / toolkit change that
+ * breaks a descriptor encoding shows up as a wrong tile rather than as wrong gradients.
+ *   form 0: C[128,128] = A[128,D] * B[128,D]^T      (both operands row-major, "K-major")
+ *   form 1: C[128,D]   = P[128,128] * B[128,D]      (P from tensor memory, B row-major)
+ *   form 2: C[128,D]   = A[128,128]^T * B[128,D]    (A staged transposed in shared memory)
+ * a, b: 16-bit inputs of `dtype`; c: fp32 output.  No counterpart in the reference.
+ */
+int fa2_selftest_mma(int form, const void* a, const void* b, float* c,
+                     int D, int dtype, fa2_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FA2_B200_H_ */
