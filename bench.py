@@ -1,0 +1,402 @@
+"""Benchmark of the causal attention forward + backward hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c3|c2|c5|c4] [--deterministic] [--scaling weak|strong]
+
+A "step" is one forward + backward (forward, preprocess, backward main, plus memset/convert
+in the atomic mode) over one batch of seeded synthetic inputs of the workload's shape.
+Default workload: bf16, q,k,v,dO [B=2, H=32, N=8192, d=128], iid N(0,1), scale 1/sqrt(128).
+
+Printed JSON (one line, rank 0):
+  value        whole-job causal fwd+bwd TFLOP/s with inputs resident in HBM, all kernels launched
+               through the C ABI on preallocated buffers, timed with CUDA events, max over ranks.
+               FLOPs = 3.5 * 4*B*H*N^2*d/2 (FlashAttention convention, causal-halved; the extra
+               recompute of the deterministic two-kernel backward is not counted).
+  e2e          same metric through flash_attention_v2(...).backward() starting from pinned HOST
+               tensors: host->device copies of q,k,v,dO and device->host copies of o,dq,dk,dv are
+               inside the timed region.
+  roofline     tensor-core roofline of the dominant kernel (backward main), achieved = its
+               algorithmic FLOPs / its own average launch duration (CUDA events around that
+               launch), peak = MEASURED_PEAKS.json bf16_tflops (burst; kernel timed alone).
+  cpu_baseline naive fp32 PyTorch causal attention fwd+bwd on the host cores over a bounded
+               sample of the same workload's heads (rank 0, N=1 only).
+
+Multi-GPU: one process per GPU (torchrun); every (batch, head) problem is independent, so
+ranks share nothing on the data path.  --scaling weak (default): every rank runs the whole
+workload shape on its own data; --scaling strong: the workload's B*H problems are split
+across ranks (shard_slab).  --impl reference times the CPU oracle (the reference has no CPU
+implementation of its own; the oracle restates its test-suite formula) on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: (B, H, N, D, dtype, qk_mul, scale)
+    "c2": (4, 16, 2048, 64, torch.float16, 1.0, None),
+    "c3": (2, 32, 8192, 128, torch.bfloat16, 1.0, None),
+    "c4": (1, 16, 32768, 128, torch.bfloat16, 1.0, None),
+    "c5": (8, 12, 4095, 32, torch.float16, 3.0, 0.5),
+}
+METRIC = "causal attn fwd+bwd TFLOP/s, bf16 N=8192 d=128"
+
+
+def fwd_flops(b, h, n, d):
+    return 4.0 * b * h * n * n * d / 2.0
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        j = json.loads(p.read_text())
+        return {"bf16": float(j["bf16_tflops"]), "bf16_sustained": float(j["bf16_tflops_sustained"]),
+                "hbm": float(j["hbm_gbs"]), "source": "measured"}
+    return {"bf16": 1590.0, "bf16_sustained": 1400.0, "hbm": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # NVML missing: clocks are reported as null
+            self.nvml = None
+
+    def _run(self):
+        n = self.nvml
+        names = {
+            "hw_slowdown": getattr(n, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(n, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(n, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(n, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM))
+                mask = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def __enter__(self):
+        if self.nvml:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+def make_inputs(shape, dtype, seed, qk_mul):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    q, k, v, do = (torch.randn(*shape, generator=g) for _ in range(4))
+    return tuple((t * m).to(dtype) for t, m in ((q, qk_mul), (k, qk_mul), (v, 1.0), (do, 1.0)))
+
+
+def cpu_baseline(b, h, n, d, dtype, qk_mul, scale, budget_s=12.0, max_heads=32):
+    """Naive fp32 causal attention fwd+bwd (the oracle), one head at a time, on all host threads."""
+    from oracle.attention_oracle import naive_attention
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v, do = make_inputs((1, 1, n, d), dtype, 123, qk_mul)
+    naive_attention(q, k, v, do, scale, torch.float32)  # warm-up
+    heads, t0 = 0, time.perf_counter()
+    while heads < max_heads and (heads == 0 or time.perf_counter() - t0 < budget_s):
+        naive_attention(q, k, v, do, scale, torch.float32)
+        heads += 1
+    el = time.perf_counter() - t0
+    tf = 3.5 * fwd_flops(1, 1, n, d) * heads / el / 1e12
+    return {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{heads} of {b * h} (batch,head) problems of the workload, fp32 naive "
+                      f"attention + analytic backward, {el:.1f} s"}
+
+
+def run_reference_arm(args, rank, world):
+    wl = WORKLOADS[args.workload]
+    b, h, n, d, dtype, qk_mul, scale = wl
+    if rank != 0:
+        return
+    from oracle.attention_oracle import naive_attention
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    heads_per_step = 1 if n >= 8192 else max(1, min(b * h, (8192 // n) ** 2))
+    q, k, v, do = make_inputs((1, heads_per_step, n, d), dtype, 123, qk_mul)
+    for _ in range(args.warmup):
+        naive_attention(q[:, :1], k[:, :1], v[:, :1], do[:, :1], scale, torch.float32)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        for hh in range(heads_per_step):
+            naive_attention(q[:, hh:hh + 1], k[:, hh:hh + 1], v[:, hh:hh + 1], do[:, hh:hh + 1],
+                            scale, torch.float32)
+    el = time.perf_counter() - t0
+    tf = 3.5 * fwd_flops(1, heads_per_step, n, d) * args.steps / el / 1e12
+    sample = (f"each step = {heads_per_step} of the workload's {b * h} (batch,head) problems, "
+              "fp32 naive attention + analytic backward on host cores")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": el / args.steps * 1e3,
+        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args, wl, world),
+        "cpu_baseline": {"value": tf, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": tf, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, wl, world):
+    b, h, n, d, dtype, qk_mul, scale = wl
+    return {
+        "workload": f"{args.workload}: causal self-attention fwd+bwd, q,k,v,dO [B={b},H={h},N={n},d={d}] "
+                    f"{str(dtype)[6:]}, iid N(0,{qk_mul:g}) q,k / N(0,1) v,dO, scale "
+                    f"{scale if scale else '1/sqrt(d)'}",
+        "deterministic": bool(args.deterministic),
+        "batch_heads_per_gpu": b * h if args.scaling == "weak" else f"{b * h}/{world}",
+        "l2": "inputs (4 x %.0f MB per step) exceed the 126 MB L2; no explicit flush" % (b * h * n * d * 2 / 1e6),
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--deterministic", action="store_true")
+    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank, world)
+        return
+
+    import torch.distributed as dist
+
+    from flash_attention_triton_b200 import _lib, flash_attention_v2, shard_slab
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    wl = WORKLOADS[args.workload]
+    b, h, n, d, dtype, qk_mul, scale_opt = wl
+    scale = scale_opt or 1.0 / math.sqrt(d)
+    code = 0 if dtype == torch.float16 else 1
+    det = int(args.deterministic)
+
+    # Inputs: seeded on the CPU, then moved.  weak: each rank its own seed, whole shape.
+    # strong: one global tensor (seed 0), each rank takes its contiguous (batch, head) slab.
+    if args.scaling == "weak":
+        host = make_inputs((b, h, n, d), dtype, rank, qk_mul)
+    else:
+        host = tuple(shard_slab(t, world, rank).contiguous() for t in make_inputs((b, h, n, d), dtype, 0, qk_mul))
+    host = tuple(t.pin_memory() for t in host)
+    lb, lh = host[0].shape[0], host[0].shape[1]
+    my_fwd_flops = fwd_flops(lb, lh, n, d)
+
+    lib = _lib.lib()
+    q, k, v, do = (t.to(dev) for t in host)
+    o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
+    lse = torch.empty(lb, lh, n, device=dev, dtype=torch.float32)
+    rowstats = torch.empty(lib.fa2_rowstats_bytes(lb, lh, n) // 4, device=dev, dtype=torch.float32)
+    wsb = lib.fa2_bwd_workspace_bytes(lb, lh, n, d, det)
+    ws = torch.empty(max(wsb // 4, 4), device=dev, dtype=torch.float32)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def k_fwd():
+        _lib.check("fa2_fwd", lib.fa2_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                                          lse.data_ptr(), lb, lh, n, d, code, scale, stream))
+
+    def k_pre():
+        _lib.check("fa2_bwd_preprocess", lib.fa2_bwd_preprocess(
+            o.data_ptr(), do.data_ptr(), lse.data_ptr(), rowstats.data_ptr(), lb, lh, n, d, code, stream))
+
+    def k_bwd():
+        _lib.check("fa2_bwd", lib.fa2_bwd(
+            q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), rowstats.data_ptr(),
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr() if wsb else None,
+            lb, lh, n, d, code, scale, det, stream))
+
+    def step():
+        k_fwd()
+        k_pre()
+        k_bwd()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    total_fwd_flops = sum_over_ranks(my_fwd_flops)
+
+    for _ in range(args.warmup):
+        step()
+    st = _lib.device_status()
+    if st != 0:
+        raise RuntimeError(f"kernel status word {st:#x} after warm-up")
+
+    # ------------------------------------------------------------ timed region (device-resident)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    with ClockSampler(local_rank) as clocks:
+        ev0.record()
+        for _ in range(args.steps):
+            step()
+        ev1.record()
+        torch.cuda.synchronize()
+    barrier()
+    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
+    ms_per_step = ms_total / args.steps
+    value = 3.5 * total_fwd_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ------------------------------------------------------------ per-kernel breakdown
+    def time_kernel(fn):
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+               for _ in range(args.steps)]
+        torch.cuda.synchronize()
+        for a, bb in evs:
+            a.record()
+            fn()
+            bb.record()
+        torch.cuda.synchronize()
+        return sum(a.elapsed_time(bb) for a, bb in evs) / len(evs)
+
+    ms_fwd = max_over_ranks(time_kernel(k_fwd))
+    ms_pre = max_over_ranks(time_kernel(k_pre))
+    ms_bwd = max_over_ranks(time_kernel(k_bwd))
+    peaks = load_peaks()
+    bwd_tf = 2.5 * my_fwd_flops / (ms_bwd * 1e-3) / 1e12
+    fwd_tf = my_fwd_flops / (ms_fwd * 1e-3) / 1e12
+    pre_bytes = 2.0 * lb * lh * n * d * 2 + lb * lh * n * 4 * 3
+    roofline = {
+        "kernel": "bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert" if not det
+                  else "bwd_dkdv_kernel + bwd_dq_kernel",
+        "bound": "tensor", "achieved": bwd_tf, "peak": peaks["bf16"], "unit": "TFLOP/s",
+        "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} burst bf16 GEMM",
+        "traffic": None,
+        "fwd": {"achieved": fwd_tf, "frac": fwd_tf / peaks["bf16"], "ms": ms_fwd},
+        "bwd_ms": ms_bwd,
+        "preprocess": {"bound": "hbm", "achieved": pre_bytes / (ms_pre * 1e-3) / 1e9,
+                       "peak": peaks["hbm"], "unit": "GB/s",
+                       "frac": pre_bytes / (ms_pre * 1e-3) / 1e9 / peaks["hbm"], "ms": ms_pre},
+    }
+
+    # ------------------------------------------------------------ end to end (host buffers)
+    e2e = None
+    if not args.no_e2e:
+        outs_host = [torch.empty(q.shape, dtype=dtype).pin_memory() for _ in range(4)]
+
+        def e2e_step():
+            qd, kd, vd, dod = (t.to(dev, non_blocking=True) for t in host)
+            qd.requires_grad_(True)
+            kd.requires_grad_(True)
+            vd.requires_grad_(True)
+            out = flash_attention_v2(qd, kd, vd, scale_opt, bool(det))
+            out.backward(dod)
+            for dst, src in zip(outs_host, (out.detach(), qd.grad, kd.grad, vd.grad)):
+                dst.copy_(src, non_blocking=True)
+
+        for _ in range(2):
+            e2e_step()
+        e_steps = max(3, min(args.steps, 10))
+        barrier()
+        ev0.record()
+        for _ in range(e_steps):
+            e2e_step()
+        ev1.record()
+        torch.cuda.synchronize()
+        barrier()
+        e_ms = max_over_ranks(ev0.elapsed_time(ev1)) / e_steps
+        nbytes = q.numel() * q.element_size()
+        e2e = {"value": 3.5 * total_fwd_flops / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "ms_per_step": e_ms, "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes}
+
+    st = _lib.device_status()
+    if st != 0:
+        raise RuntimeError(f"kernel status word {st:#x} after the timed region")
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": args.scaling, "vs_baseline": None, "dtype": str(dtype)[6:].replace("bfloat16", "bf16").replace("float16", "fp16"),
+            "data": "synthetic", "config": workload_config(args, wl, world),
+            "per_gpu_tflops": value / world,
+            "frac_of_peak": {"burst": value / world / peaks["bf16"],
+                             "sustained": value / world / peaks["bf16_sustained"],
+                             "nominal_2250": value / world / 2250.0, "source": peaks["source"]},
+            "clocks": clocks.summary(),
+            "gpu_launches": 4 * args.steps,
+            "roofline": roofline,
+            "e2e": e2e,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(b, h, n, d, dtype, qk_mul, scale_opt)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,95 @@
+"""The C-ABI shared library: loads without a GPU, exports every symbol the header declares,
+and rejects bad arguments with the documented codes before touching the device."""
+
+from __future__ import annotations
+
+import ctypes
+import re
+
+import pytest
+
+from conftest import ROOT
+from flash_attention_triton_b200 import _lib
+
+HEADER = ROOT / "include" / "fa2_b200.h"
+
+
+def declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(fa2_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_hot_path_entry_points():
+    names = declared_functions()
+    for need in ("fa2_fwd", "fa2_bwd_preprocess", "fa2_bwd", "fa2_bwd_workspace_bytes",
+                 "fa2_rowstats_bytes", "fa2_strerror", "fa2_abi_version", "fa2_device_status"):
+        assert need in names
+
+
+def test_library_exports_every_declared_symbol():
+    handle = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in declared_functions():
+        assert hasattr(handle, name), f"{name} is declared in the header but not exported"
+
+
+def test_binding_table_covers_header():
+    assert sorted(n for n, _, _ in _lib.SYMBOLS) == declared_functions()
+
+
+def test_abi_version_and_error_text():
+    lib = _lib.lib()
+    assert lib.fa2_abi_version() == 1
+    assert lib.fa2_strerror(0) == b"success"
+    assert b"32, 64 or 128" in lib.fa2_strerror(-2)
+    assert lib.fa2_strerror(-12345) == b"unknown fa2 error code"
+
+
+def test_size_queries():
+    lib = _lib.lib()
+    # rowstats: [B*H][ceil(N/128)][2][128] fp32
+    assert lib.fa2_rowstats_bytes(2, 3, 4095) == 2 * 3 * 32 * 256 * 4
+    assert lib.fa2_rowstats_bytes(0, 3, 128) == 0
+    # dq workspace: fp32 [B*H][ceil(N/128)*128][D], none in deterministic mode
+    assert lib.fa2_bwd_workspace_bytes(2, 3, 4095, 32, 0) == 2 * 3 * 4096 * 32 * 4
+    assert lib.fa2_bwd_workspace_bytes(2, 3, 4095, 32, 1) == 0
+
+
+@pytest.mark.parametrize(
+    "kwargs, code",
+    [
+        (dict(q=0), -1),                      # NULL pointer
+        (dict(D=48), -2),                     # unsupported head dim
+        (dict(dtype=7), -3),                  # unsupported dtype
+        (dict(q=0x1008), -4),                 # misaligned pointer
+        (dict(N=0), -5),                      # empty sequence
+        (dict(B=70000), -5),                  # B*H > 65535
+        (dict(scale=float("nan")), -9),
+        (dict(scale=-1.0), -9),
+    ],
+)
+def test_forward_argument_errors_need_no_gpu(kwargs, code):
+    a = dict(q=0x1000, k=0x2000, v=0x3000, o=0x4000, lse=0x5000, B=1, H=1, N=128, D=64, dtype=0,
+             scale=0.125)
+    a.update(kwargs)
+    rc = _lib.lib().fa2_fwd(a["q"], a["k"], a["v"], a["o"], a["lse"], a["B"], a["H"], a["N"],
+                            a["D"], a["dtype"], a["scale"], None)
+    assert rc == code
+
+
+def test_backward_argument_errors_need_no_gpu():
+    lib = _lib.lib()
+    p = [0x1000 * (i + 1) for i in range(8)]
+    # non-deterministic mode without a workspace
+    rc = lib.fa2_bwd(*p[:5], p[5], p[6], p[7], None, 1, 1, 128, 64, 0, 0.125, 0, None)
+    assert rc == -10
+    rc = lib.fa2_bwd(*p[:5], p[5], p[6], None, None, 1, 1, 128, 64, 0, 0.125, 1, None)
+    assert rc == -1
+    rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], None, 1, 1, 128, 64, 0, None)
+    assert rc == -1
+    rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], p[3], 1, 1, 128, 96, 0, None)
+    assert rc == -2
+
+
+def test_check_raises_with_text():
+    with pytest.raises(_lib.Fa2Error, match="head dimension"):
+        _lib.check("fa2_fwd", -2)

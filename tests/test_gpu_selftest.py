@@ -1,0 +1,31 @@
+"""Single-tile tensor-core self-test through the C ABI: each operand form the attention
+kernels rely on (K-major shared memory, tensor-memory A operand, MN-major shared memory)
+against a plain fp64 matrix product."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+from flash_attention_triton_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16], ids=["fp16", "bf16"])
+@pytest.mark.parametrize("d", [32, 64, 128])
+@pytest.mark.parametrize("form", [0, 1, 2])
+def test_mma_operand_forms(form, d, dtype):
+    g = torch.Generator().manual_seed(100 * form + d)
+    a = torch.randn(128, d if form == 0 else 128, generator=g).to(dtype)
+    b = torch.randn(128, d, generator=g).to(dtype)
+    ref = {0: a.double() @ b.double().T, 1: a.double() @ b.double(), 2: a.double().T @ b.double()}[form]
+    ad, bd = a.cuda(), b.cuda()
+    c = torch.full(ref.shape, float("nan"), device="cuda", dtype=torch.float32)
+    rc = _lib.lib().fa2_selftest_mma(form, ad.data_ptr(), bd.data_ptr(), c.data_ptr(), d,
+                                     0 if dtype == torch.float16 else 1,
+                                     torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    assert _lib.device_status() == 0
+    # fp32 accumulation of exact 16-bit products: error is a few fp32 ulps of the result
+    assert (c.cpu().double() - ref).abs().max().item() < 1e-3

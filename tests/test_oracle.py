@@ -19,18 +19,24 @@ def test_golden_files_present():
 
 @pytest.mark.parametrize("path", GOLDEN, ids=lambda p: p.stem)
 def test_restatement_matches_reference_kernels(path):
-    """The numpy restatement reproduces the reference kernels to two fp16 ulps (bit-exact for
-    three of the four cases; BLAS blocking may reorder a 128-long fp32 sum in the fourth)."""
+    """The numpy restatement reproduces the reference kernels: bit-exact for three of the four
+    cases; in the d=128 case BLAS blocking reorders a 128-long fp32 sum, which can move a
+    result across an fp16 rounding boundary, so the bound is one fp16 ulp (2^-10 relative,
+    5e-4 absolute near zero)."""
     z = np.load(path)
     r = reference_tiled(
         z["q"], z["k"], z["v"], z["dout"], float(z["softmax_scale"]),
         int(z["fwd_block"]), int(z["fwd_block"]), int(z["bwd_block"]),
     )
+    exact = "d128" not in path.stem
     for key in ("o", "dq", "dk", "dv"):
-        got, want = r[key].astype(np.float32), z[key].astype(np.float32)
-        ulp = np.spacing(np.maximum(np.abs(want), np.abs(got)).astype(np.float16)).astype(np.float32)
-        assert np.all(np.abs(got - want) <= 2 * ulp), key
-    np.testing.assert_allclose(r["lse"], z["lse"], rtol=0, atol=2e-6)
+        if exact:
+            assert np.array_equal(r[key], z[key]), key
+        else:
+            np.testing.assert_allclose(
+                r[key].astype(np.float32), z[key].astype(np.float32), rtol=2**-10, atol=5e-4
+            )
+    np.testing.assert_allclose(r["lse"], z["lse"], rtol=0, atol=0 if exact else 2e-6)
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=lambda p: p.stem)
