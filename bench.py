@@ -50,6 +50,8 @@ WORKLOADS = {
     "c3": (2, 32, 8192, 128, torch.bfloat16, 1.0, None),
     "c4": (1, 16, 32768, 128, torch.bfloat16, 1.0, None),
     "c5": (8, 12, 4095, 32, torch.float16, 3.0, 0.5),
+    # reduced C3 (same N, d, dtype; 24 instead of 64 batch*heads) for profiler captures
+    "c3small": (1, 24, 8192, 128, torch.bfloat16, 1.0, None),
 }
 METRIC = "causal attn fwd+bwd TFLOP/s, bf16 N=8192 d=128"
 

@@ -19,9 +19,10 @@
 // accumulates dQ_i over ascending j in tensor memory, so each dQ tile has one owner and one
 // summation order.
 //
-// lse*log2(e) and delta of a Q tile arrive in shared memory as one 1 KiB bulk copy from the
-// tile-blocked rowstats array; padded rows carry lse = +inf, which makes their P exactly 0.
+// -lse*log2(e) and -delta of a Q tile arrive in shared memory as one 1 KiB bulk copy from the
+// tile-blocked rowstats array; padded rows carry -lse = -inf, which makes their P exactly 0.
 #include "common.cuh"
+#include "mma_issue.cuh"
 #include "ptx.cuh"
 
 namespace fa2 {
@@ -40,11 +41,6 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
                "f"(d)
                : "memory");
 }
-
-// Tensor-memory column of the 16-bit operand for MMA step k (16 of the 128 reduction indices):
-// compute group 0 packs indices 0..63 into columns 0..31 of the region, group 1 packs indices
-// 64..127 into columns 64..95 (each group only overwrites columns it has already read).
-__device__ __forceinline__ uint32_t packed_col(int k) { return (k < 4) ? k * 8 : 64 + (k - 4) * 8; }
 
 // Epilogue helper: one warp converts its 32 rows of a [128, D] fp32 accumulator to 16 bits,
 // stages them swizzled in `stage` (a free tile buffer) and stores them with one TMA per chunk.
@@ -107,10 +103,10 @@ struct DkdvCfg {
   static constexpr int kBarDOEmpty = kBarDOFull + kStages;
   static constexpr int kBarStFull = kBarDOEmpty + kStages;
   static constexpr int kBarDptFull = kBarStFull + 1;
-  static constexpr int kBarPtReady = kBarDptFull + 1;   // 256 arrivals
-  static constexpr int kBarDsReady = kBarPtReady + 1;   // 256 arrivals
+  static constexpr int kBarPtReady = kBarDptFull + 1;   // 8 arrivals (one per compute warp)
+  static constexpr int kBarDsReady = kBarPtReady + 1;   // 8 arrivals
   static constexpr int kBarDqFull = kBarDsReady + 1;
-  static constexpr int kBarDqDrained = kBarDqFull + 1;  // 128 arrivals
+  static constexpr int kBarDqDrained = kBarDqFull + 1;  // 4 arrivals
   static constexpr int kBarDone = kBarDqDrained + 1;
   static constexpr int kNumBars = kBarDone + 1;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
@@ -175,10 +171,10 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
     }
     mbar_init(bar(C::kBarStFull), 1);
     mbar_init(bar(C::kBarDptFull), 1);
-    mbar_init(bar(C::kBarPtReady), 256);
-    mbar_init(bar(C::kBarDsReady), 256);
+    mbar_init(bar(C::kBarPtReady), 8);
+    mbar_init(bar(C::kBarDsReady), 8);
     mbar_init(bar(C::kBarDqFull), 1);
-    mbar_init(bar(C::kBarDqDrained), 128);
+    mbar_init(bar(C::kBarDqDrained), 4);
     mbar_init(bar(C::kBarDone), 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -196,6 +192,7 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
 
   if (warp >= C::kMmaWarp) {
     // ---------------------------------------------------------------- producer / MMA group
+    reg_dec<64>();
     if (warp == C::kLoadWarp && lane == 0) {
       prefetch_tensormap(&tq);
       prefetch_tensormap(&tk);
@@ -226,28 +223,14 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
                       ch * T::kChunkElems, qt * 128, bh, bar(C::kBarDOFull + s));
       }
     } else if (warp == C::kMmaWarp && lane == 0) {
-      constexpr uint32_t idesc_t = make_idesc(128, 128, BF16, false, false);   // St, dPt
-      constexpr uint32_t idesc_acc = make_idesc(128, D, BF16, false, true);    // dV, dK
-      constexpr uint32_t idesc_dq = make_idesc(128, D, BF16, true, true);      // dQ
       const uint32_t ka = smem_base + C::kOffK, va = smem_base + C::kOffV;
-      // D[128 kv, 128 q] = A[kv, d] * B[q, d]^T, both K-major
+      // St / dPt: [128 kv, 128 q] = (K or V tile) x (Q or dO tile)^T, both K-major.
       auto issue_t = [&](uint32_t col, uint32_t a_base, uint32_t b_base) {
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off =
-              (k / T::kKStepsPerChunk) * T::kChunkTileBytes + (k % T::kKStepsPerChunk) * 32;
-          mma_ss(tmem_base + col, make_smem_desc(a_base + off, 16, T::kAtomBytes, T::kSwizzleMode),
-                 make_smem_desc(b_base + off, 16, T::kAtomBytes, T::kSwizzleMode), idesc_t, k > 0);
-        }
+        issue_rows_x_rows<D, BF16>(tmem_base + col, a_base, b_base);
       };
-      // D[128 kv, D] += A[kv, q](tmem, 16-bit) * B[q, d] (MN-major tile of Q or dO)
+      // dV / dK: [128 kv, D] += (16-bit Pt or dSt in tensor memory) x (dO or Q tile, MN-major).
       auto issue_acc = [&](uint32_t col_d, uint32_t col_a, uint32_t b_base, bool accumulate) {
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          mma_ts(tmem_base + col_d, tmem_base + col_a + packed_col(k),
-                 make_smem_desc(b_base + k * 2 * T::kAtomBytes, T::kChunkTileBytes, T::kAtomBytes,
-                                T::kSwizzleMode),
-                 idesc_acc, (accumulate || k > 0) ? 1u : 0u);
+        issue_tmem_x_tile<D, BF16>(tmem_base + col_d, tmem_base + col_a, 64, b_base, accumulate);
       };
       bool ok = mbar_wait(bar(C::kBarKV), 0, w, kBSiteMmaKV) &&
                 mbar_wait(bar(C::kBarQFull + 0), 0, w, kBSiteMmaQ);
@@ -281,13 +264,7 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
         if constexpr (FUSE) {
           // dQ_i[128 q, D] = dS[q, kv] * K[kv, d]: A = dS^T tile in smem (q contiguous ->
           // MN-major), B = K tile (d contiguous -> MN-major); 16 kv rows per MMA.
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            mma_ss(tmem_base + C::kColDpt,
-                   make_smem_desc(smem_base + C::kOffDS + k * 2048, 16384, 1024, kSwizzle128B),
-                   make_smem_desc(ka + k * 2 * T::kAtomBytes, T::kChunkTileBytes, T::kAtomBytes,
-                                  T::kSwizzleMode),
-                   idesc_dq, k > 0);
+          issue_tileT_x_tile<D, BF16>(tmem_base + C::kColDpt, smem_base + C::kOffDS, ka);
           mma_commit(bar(C::kBarDqFull));
         }
         if (ii + 1 < nq) {
@@ -305,6 +282,7 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
     __syncwarp();
   } else if (FUSE && warp >= 8) {
     // ---------------------------------------------------------------- dQ reduction group
+    reg_dec<104>();
     const int w4 = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
     for (int ii = 0; ii < nq; ++ii) {
@@ -321,7 +299,8 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
         tmem_wait_ld();
         if (c0 + 64 >= D) {  // whole tile is in registers: the MMA warp may overwrite it
           tc_fence_before();
-          mbar_arrive(bar(C::kBarDqDrained));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(C::kBarDqDrained));
         }
 #pragma unroll
         for (int k = 0; k < (D > 32 ? 16 : 8); ++k)
@@ -332,22 +311,25 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
     }
   } else {
     // ---------------------------------------------------------------- compute groups
+    if constexpr (FUSE) reg_inc<168>(); else reg_inc<208>();
     const int wg = warp >> 2;  // 0: score columns (q) 0..63, 1: 64..127
     const int w4 = warp & 3;
     const int r = w4 * 32 + lane;  // kv row in the tile = tensor-memory lane
     const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
     const uint32_t tSt = tmem_base + lane_base + C::kColSt + wg * 64;
     const uint32_t tDpt = tmem_base + lane_base + C::kColDpt + wg * 64;
+    const float2 sc2 = make_float2(scale_log2, scale_log2);
+    const float2 scale2 = make_float2(scale, scale);
     bool ok = true;
     for (int ii = 0; ii < nq; ++ii) {
       const int s = ii % C::kStages, ph = (ii / C::kStages) & 1;
       const float* stats = reinterpret_cast<const float*>(smem + C::kOffStats + s * 1024);
-      const float4* lse2 = reinterpret_cast<const float4*>(stats + wg * 64);
-      const float4* dlt = reinterpret_cast<const float4*>(stats + 128 + wg * 64);
+      const float4* nlse = reinterpret_cast<const float4*>(stats + wg * 64);        // -lse*log2e
+      const float4* ndlt = reinterpret_cast<const float4*>(stats + 128 + wg * 64);  // -delta
       if (!(ok = mbar_wait_warp(bar(C::kBarQFull + s), ph, w, kBSiteCmpQ))) break;
       if (!(ok = mbar_wait_warp(bar(C::kBarStFull), ii & 1, w, kBSiteCmpSt))) break;
       tc_fence_after();
-      float p[64];
+      float2 p[32];  // P^T for this thread's kv row, q columns wg*64 .. wg*64+63
       {
         uint32_t sr[64];
         tmem_ld_x32(tSt, sr);
@@ -355,26 +337,32 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
         tmem_wait_ld();
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 l = lse2[c4];
-          p[4 * c4 + 0] = ex2(fmaf(__uint_as_float(sr[4 * c4 + 0]), scale_log2, -l.x));
-          p[4 * c4 + 1] = ex2(fmaf(__uint_as_float(sr[4 * c4 + 1]), scale_log2, -l.y));
-          p[4 * c4 + 2] = ex2(fmaf(__uint_as_float(sr[4 * c4 + 2]), scale_log2, -l.z));
-          p[4 * c4 + 3] = ex2(fmaf(__uint_as_float(sr[4 * c4 + 3]), scale_log2, -l.w));
+          const float4 l = nlse[c4];
+          float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4]), __uint_as_float(sr[4 * c4 + 1])),
+                                 sc2, make_float2(l.x, l.y));
+          float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4 + 2]), __uint_as_float(sr[4 * c4 + 3])),
+                                 sc2, make_float2(l.z, l.w));
+          p[2 * c4] = make_float2(ex2(t0.x), ex2(t0.y));
+          p[2 * c4 + 1] = make_float2(ex2(t1.x), ex2(t1.y));
         }
       }
       if (ii == 0) {  // diagonal tile: keep q >= kv
 #pragma unroll
-        for (int c = 0; c < 64; ++c) p[c] = (wg * 64 + c >= r) ? p[c] : 0.f;
+        for (int c = 0; c < 32; ++c) {
+          p[c].x = (wg * 64 + 2 * c >= r) ? p[c].x : 0.f;
+          p[c].y = (wg * 64 + 2 * c + 1 >= r) ? p[c].y : 0.f;
+        }
       }
       {
         uint32_t pk[32];
 #pragma unroll
-        for (int c = 0; c < 32; ++c) pk[c] = pack2<BF16>(p[2 * c], p[2 * c + 1]);
+        for (int c = 0; c < 32; ++c) pk[c] = pack2<BF16>(p[c].x, p[c].y);
         tmem_st_x32(tSt, pk);  // columns wg*64 .. wg*64+31 of the St region
         tmem_wait_st();
       }
       tc_fence_before();
-      mbar_arrive(bar(C::kBarPtReady));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarPtReady));
 
       if (!(ok = mbar_wait_warp(bar(C::kBarDptFull), ii & 1, w, kBSiteCmpDpt))) break;
       tc_fence_after();
@@ -386,14 +374,16 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
         tmem_wait_ld();
 #pragma unroll
         for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 dl = dlt[8 * h + c4];
-          const int c = 32 * h + 4 * c4;
-          const float d0 = p[c + 0] * (__uint_as_float(dp[4 * c4 + 0]) - dl.x) * scale;
-          const float d1 = p[c + 1] * (__uint_as_float(dp[4 * c4 + 1]) - dl.y) * scale;
-          const float d2 = p[c + 2] * (__uint_as_float(dp[4 * c4 + 2]) - dl.z) * scale;
-          const float d3 = p[c + 3] * (__uint_as_float(dp[4 * c4 + 3]) - dl.w) * scale;
-          dsk[16 * h + 2 * c4] = pack2<BF16>(d0, d1);
-          dsk[16 * h + 2 * c4 + 1] = pack2<BF16>(d2, d3);
+          const float4 nd = ndlt[8 * h + c4];
+          // dS = P * (dP - delta) * scale, scale folded in before the 16-bit rounding
+          float2 u0 = __fadd2_rn(make_float2(__uint_as_float(dp[4 * c4]), __uint_as_float(dp[4 * c4 + 1])),
+                                 make_float2(nd.x, nd.y));
+          float2 u1 = __fadd2_rn(make_float2(__uint_as_float(dp[4 * c4 + 2]), __uint_as_float(dp[4 * c4 + 3])),
+                                 make_float2(nd.z, nd.w));
+          u0 = __fmul2_rn(__fmul2_rn(p[16 * h + 2 * c4], u0), scale2);
+          u1 = __fmul2_rn(__fmul2_rn(p[16 * h + 2 * c4 + 1], u1), scale2);
+          dsk[16 * h + 2 * c4] = pack2<BF16>(u0.x, u0.y);
+          dsk[16 * h + 2 * c4 + 1] = pack2<BF16>(u1.x, u1.y);
         }
       }
       tmem_st_x32(tDpt, dsk);  // columns 128 + wg*64 .. +31
@@ -407,7 +397,8 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(C::kBarDsReady));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarDsReady));
     }
     // epilogue: group 0 stores dV, group 1 stores dK, staged through the idle dO / Q buffers
     if (ok && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
@@ -432,33 +423,41 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
 // =========================================================================================
 // dQ kernel (deterministic path): one CTA per Q tile, KV tiles in ascending order
 // =========================================================================================
+// Pipeline per KV tile j:  S(j) = Q K_j^T lands in score buffer j%2, dP(j) = dO V_j^T in the dP
+// columns.  The compute warps turn S into P (registers), read dP, release the dP columns
+// (so dP(j+1) can be issued while they still work), write dS(j) as 16-bit pairs over the score
+// buffer they just read, and the MMA warp then issues dQ += dS(j) K_j followed by S(j+2) into
+// the same buffer.  S(j+1) is already in the other buffer, so the tensor pipe and the compute
+// warps overlap instead of alternating.
 template <int D>
 struct DqCfg {
   using T = Tile<D>;
-  static constexpr int kStages = 2;  // K ring and V ring
+  static constexpr int kKStages = 3;  // K_j is needed by S(j) and, later, by dQ(j)
+  static constexpr int kVStages = 2;
   static constexpr int kThreads = 384;
   static constexpr int kMmaWarp = 8;
   static constexpr int kLoadWarp = 9;
   static constexpr int kOffQ = 0;
   static constexpr int kOffDO = kOffQ + T::kTileBytes;
   static constexpr int kOffK = kOffDO + T::kTileBytes;
-  static constexpr int kOffV = kOffK + kStages * T::kTileBytes;
-  static constexpr int kOffStats = kOffV + kStages * T::kTileBytes;  // [256] fp32
+  static constexpr int kOffV = kOffK + kKStages * T::kTileBytes;
+  static constexpr int kOffStats = kOffV + kVStages * T::kTileBytes;  // [256] fp32
   static constexpr int kOffBar = kOffStats + 1024;
   static constexpr int kBarQ = 0;  // Q, dO and rowstats
   static constexpr int kBarKFull = 1;
-  static constexpr int kBarKEmpty = kBarKFull + kStages;
-  static constexpr int kBarVFull = kBarKEmpty + kStages;
-  static constexpr int kBarVEmpty = kBarVFull + kStages;
-  static constexpr int kBarSFull = kBarVEmpty + kStages;
-  static constexpr int kBarDpFull = kBarSFull + 1;
-  static constexpr int kBarDsReady = kBarDpFull + 1;  // 256 arrivals
+  static constexpr int kBarKEmpty = kBarKFull + kKStages;
+  static constexpr int kBarVFull = kBarKEmpty + kKStages;
+  static constexpr int kBarVEmpty = kBarVFull + kVStages;
+  static constexpr int kBarSFull = kBarVEmpty + kVStages;  // 2 (one per score buffer)
+  static constexpr int kBarDpFull = kBarSFull + 2;
+  static constexpr int kBarDpConsumed = kBarDpFull + 1;  // 8 arrivals (one per compute warp)
+  static constexpr int kBarDsReady = kBarDpConsumed + 1;  // 8 arrivals
   static constexpr int kBarDone = kBarDsReady + 1;
   static constexpr int kNumBars = kBarDone + 1;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
-  static constexpr int kColS = 0;
-  static constexpr int kColDp = 128;  // dS (16-bit) is written over dP
-  static constexpr int kColDQ = 256;
+  static constexpr int kColS = 0;     // score buffers at 0 and 128; dS (16-bit) overwrites them
+  static constexpr int kColDp = 256;
+  static constexpr int kColDQ = 384;
   static constexpr int kTmemCols = 512;
 };
 
@@ -489,15 +488,19 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(bar(C::kBarQ), 1);
-    for (int i = 0; i < C::kStages; ++i) {
+    for (int i = 0; i < C::kKStages; ++i) {
       mbar_init(bar(C::kBarKFull + i), 1);
       mbar_init(bar(C::kBarKEmpty + i), 1);
+    }
+    for (int i = 0; i < C::kVStages; ++i) {
       mbar_init(bar(C::kBarVFull + i), 1);
       mbar_init(bar(C::kBarVEmpty + i), 1);
     }
-    mbar_init(bar(C::kBarSFull), 1);
+    mbar_init(bar(C::kBarSFull + 0), 1);
+    mbar_init(bar(C::kBarSFull + 1), 1);
     mbar_init(bar(C::kBarDpFull), 1);
-    mbar_init(bar(C::kBarDsReady), 256);
+    mbar_init(bar(C::kBarDpConsumed), 8);
+    mbar_init(bar(C::kBarDsReady), 8);
     mbar_init(bar(C::kBarDone), 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -514,6 +517,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
   const WaitCtx w{abort_flag, status};
 
   if (warp >= C::kMmaWarp) {
+    reg_dec<72>();
     if (warp == C::kLoadWarp && lane == 0) {
       prefetch_tensormap(&tq);
       prefetch_tensormap(&tk);
@@ -529,121 +533,132 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
       bulk_load_1d(smem_base + C::kOffStats,
                    rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024, bar(C::kBarQ));
       for (int j = 0; j < nkv; ++j) {
-        const int s = j % C::kStages, ph = (j / C::kStages) & 1;
-        if (!mbar_wait(bar(C::kBarKEmpty + s), ph ^ 1, w, kBSiteLoadQ)) break;
-        mbar_arrive_expect_tx(bar(C::kBarKFull + s), T::kTileBytes);
+        const int ks = j % C::kKStages, kph = (j / C::kKStages) & 1;
+        if (!mbar_wait(bar(C::kBarKEmpty + ks), kph ^ 1, w, kBSiteLoadQ)) break;
+        mbar_arrive_expect_tx(bar(C::kBarKFull + ks), T::kTileBytes);
         for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffK + s * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
-                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + s));
-        if (!mbar_wait(bar(C::kBarVEmpty + s), ph ^ 1, w, kBSiteLoadDO)) break;
-        mbar_arrive_expect_tx(bar(C::kBarVFull + s), T::kTileBytes);
+          tma_load_3d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
+                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + ks));
+        const int vs = j % C::kVStages, vph = (j / C::kVStages) & 1;
+        if (!mbar_wait(bar(C::kBarVEmpty + vs), vph ^ 1, w, kBSiteLoadDO)) break;
+        mbar_arrive_expect_tx(bar(C::kBarVFull + vs), T::kTileBytes);
         for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffV + s * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
-                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarVFull + s));
+          tma_load_3d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
+                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarVFull + vs));
       }
     } else if (warp == C::kMmaWarp && lane == 0) {
-      constexpr uint32_t idesc_t = make_idesc(128, 128, BF16, false, false);  // S, dP
-      constexpr uint32_t idesc_dq = make_idesc(128, D, BF16, false, true);    // dQ
       const uint32_t qa = smem_base + C::kOffQ, doa = smem_base + C::kOffDO;
-      auto issue_t = [&](uint32_t col, uint32_t a_base, uint32_t b_base) {
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off =
-              (k / T::kKStepsPerChunk) * T::kChunkTileBytes + (k % T::kKStepsPerChunk) * 32;
-          mma_ss(tmem_base + col, make_smem_desc(a_base + off, 16, T::kAtomBytes, T::kSwizzleMode),
-                 make_smem_desc(b_base + off, 16, T::kAtomBytes, T::kSwizzleMode), idesc_t, k > 0);
-        }
+      auto k_addr = [&](int j) { return smem_base + C::kOffK + (j % C::kKStages) * T::kTileBytes; };
+      auto k_wait = [&](int j) {
+        return mbar_wait(bar(C::kBarKFull + j % C::kKStages), (j / C::kKStages) & 1, w, kBSiteMmaKV);
       };
-      bool ok = mbar_wait(bar(C::kBarQ), 0, w, kBSiteMmaQ);
-      for (int j = 0; ok && j <= nkv; ++j) {
-        // issue S(j), dP(j) (if any), then dQ += dS(j-1) K_{j-1}
-        if (j < nkv) {
-          const int s = j % C::kStages, ph = (j / C::kStages) & 1;
-          if (j > 0) {
-            // S and dP regions are rewritten: dS(j-1) must have been produced from them, and
-            // the dQ MMA that reads dS(j-1) is issued first (in-order pipe).
-            if (!(ok = mbar_wait(bar(C::kBarDsReady), (j - 1) & 1, w, kBSiteMmaDs))) break;
-            tc_fence_after();
-            const int sp = (j - 1) % C::kStages;
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-              mma_ts(tmem_base + C::kColDQ, tmem_base + C::kColDp + packed_col(k),
-                     make_smem_desc(smem_base + C::kOffK + sp * T::kTileBytes + k * 2 * T::kAtomBytes,
-                                    T::kChunkTileBytes, T::kAtomBytes, T::kSwizzleMode),
-                     idesc_dq, (j > 1 || k > 0) ? 1u : 0u);
-            mma_commit(bar(C::kBarKEmpty + sp));
-          }
-          if (!(ok = mbar_wait(bar(C::kBarKFull + s), ph, w, kBSiteMmaKV))) break;
-          issue_t(C::kColS, qa, smem_base + C::kOffK + s * T::kTileBytes);
-          mma_commit(bar(C::kBarSFull));
-          if (!(ok = mbar_wait(bar(C::kBarVFull + s), ph, w, kBSiteMmaDO))) break;
-          issue_t(C::kColDp, doa, smem_base + C::kOffV + s * T::kTileBytes);
-          mma_commit(bar(C::kBarDpFull));
-          mma_commit(bar(C::kBarVEmpty + s));
-        } else {
-          if (!(ok = mbar_wait(bar(C::kBarDsReady), (j - 1) & 1, w, kBSiteMmaDs))) break;
+      auto issue_s = [&](int j) {  // S(j) -> score buffer j%2
+        issue_rows_x_rows<D, BF16>(tmem_base + C::kColS + (j & 1) * 128, qa, k_addr(j));
+        mma_commit(bar(C::kBarSFull + (j & 1)));
+      };
+      auto issue_dp = [&](int j) {  // dP(j); V_j is free afterwards
+        const int vs = j % C::kVStages;
+        issue_rows_x_rows<D, BF16>(tmem_base + C::kColDp, doa,
+                                   smem_base + C::kOffV + vs * T::kTileBytes);
+        mma_commit(bar(C::kBarDpFull));
+        mma_commit(bar(C::kBarVEmpty + vs));
+      };
+      auto v_wait = [&](int j) {
+        return mbar_wait(bar(C::kBarVFull + j % C::kVStages), (j / C::kVStages) & 1, w, kBSiteMmaDO);
+      };
+      bool ok = mbar_wait(bar(C::kBarQ), 0, w, kBSiteMmaQ) && k_wait(0);
+      if (ok) {
+        issue_s(0);
+        ok = v_wait(0);
+      }
+      if (ok) {
+        issue_dp(0);
+        if (nkv > 1 && (ok = k_wait(1))) issue_s(1);
+      }
+      for (int j = 0; ok && j < nkv; ++j) {
+        if (j + 1 < nkv) {
+          // dP columns are free once every compute warp has read dP(j)
+          if (!(ok = mbar_wait(bar(C::kBarDpConsumed), j & 1, w, kBSiteMmaDrain))) break;
           tc_fence_after();
-          const int sp = (j - 1) % C::kStages;
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            mma_ts(tmem_base + C::kColDQ, tmem_base + C::kColDp + packed_col(k),
-                   make_smem_desc(smem_base + C::kOffK + sp * T::kTileBytes + k * 2 * T::kAtomBytes,
-                                  T::kChunkTileBytes, T::kAtomBytes, T::kSwizzleMode),
-                   idesc_dq, (j > 1 || k > 0) ? 1u : 0u);
-          mma_commit(bar(C::kBarDone));
+          if (!(ok = v_wait(j + 1))) break;
+          issue_dp(j + 1);
+        }
+        if (!(ok = mbar_wait(bar(C::kBarDsReady), j & 1, w, kBSiteMmaDs))) break;
+        tc_fence_after();
+        // dQ += dS(j) K_j : A = 16-bit dS over score buffer j%2, B = K_j as MN-major tile
+        issue_tmem_x_tile<D, BF16>(tmem_base + C::kColDQ, tmem_base + C::kColS + (j & 1) * 128, 64,
+                                   k_addr(j), j > 0);
+        mma_commit(bar(C::kBarKEmpty + j % C::kKStages));
+        if (j + 2 < nkv) {
+          if (!(ok = k_wait(j + 2))) break;
+          issue_s(j + 2);  // reuses buffer j%2; ordered after dQ(j) by the in-order MMA pipe
         }
       }
+      if (ok) mma_commit(bar(C::kBarDone));
     }
     __syncwarp();
   } else {
+    reg_inc<208>();
     const int wg = warp >> 2;
     const int w4 = warp & 3;
     const int r = w4 * 32 + lane;  // q row in the tile = tensor-memory lane
     const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
-    const uint32_t tS = tmem_base + lane_base + C::kColS + wg * 64;
     const uint32_t tDp = tmem_base + lane_base + C::kColDp + wg * 64;
+    const float2 sc2 = make_float2(scale_log2, scale_log2);
+    const float2 scale2 = make_float2(scale, scale);
     bool ok = mbar_wait_warp(bar(C::kBarQ), 0, w, kBSiteCmpQ);
-    float lse2 = 0.f, dlt = 0.f;
+    float2 nlse2 = make_float2(0.f, 0.f), ndlt2 = make_float2(0.f, 0.f);
     if (ok) {
       const float* stats = reinterpret_cast<const float*>(smem + C::kOffStats);
-      lse2 = stats[r];
-      dlt = stats[128 + r];
+      nlse2 = make_float2(stats[r], stats[r]);              // -lse*log2e of this row
+      ndlt2 = make_float2(stats[128 + r], stats[128 + r]);  // -delta of this row
     }
     for (int j = 0; ok && j < nkv; ++j) {
-      if (!(ok = mbar_wait_warp(bar(C::kBarSFull), j & 1, w, kBSiteCmpSt))) break;
+      const uint32_t tS = tmem_base + lane_base + C::kColS + (j & 1) * 128 + wg * 64;
+      if (!(ok = mbar_wait_warp(bar(C::kBarSFull + (j & 1)), (j >> 1) & 1, w, kBSiteCmpSt))) break;
       tc_fence_after();
-      float p[64];
+      float2 p[32];
       {
         uint32_t sr[64];
         tmem_ld_x32(tS, sr);
         tmem_ld_x32(tS + 32, sr + 32);
         tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 64; ++c) p[c] = ex2(fmaf(__uint_as_float(sr[c]), scale_log2, -lse2));
+        for (int c = 0; c < 32; ++c) {
+          const float2 t = __ffma2_rn(
+              make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sc2, nlse2);
+          p[c] = make_float2(ex2(t.x), ex2(t.y));
+        }
       }
       if (j == qt) {  // diagonal tile: keep kv <= q
 #pragma unroll
-        for (int c = 0; c < 64; ++c) p[c] = (wg * 64 + c <= r) ? p[c] : 0.f;
+        for (int c = 0; c < 32; ++c) {
+          p[c].x = (wg * 64 + 2 * c <= r) ? p[c].x : 0.f;
+          p[c].y = (wg * 64 + 2 * c + 1 <= r) ? p[c].y : 0.f;
+        }
       }
       if (!(ok = mbar_wait_warp(bar(C::kBarDpFull), j & 1, w, kBSiteCmpDpt))) break;
       tc_fence_after();
+      uint32_t dp[64];
+      tmem_ld_x32(tDp, dp);
+      tmem_ld_x32(tDp + 32, dp + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarDpConsumed));
       uint32_t dsk[32];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t dp[32];
-        tmem_ld_x32(tDp + 32 * h, dp);
-        tmem_wait_ld();
-#pragma unroll
-        for (int c = 0; c < 16; ++c) {
-          const float d0 = p[32 * h + 2 * c] * (__uint_as_float(dp[2 * c]) - dlt) * scale;
-          const float d1 = p[32 * h + 2 * c + 1] * (__uint_as_float(dp[2 * c + 1]) - dlt) * scale;
-          dsk[16 * h + c] = pack2<BF16>(d0, d1);
-        }
+      for (int c = 0; c < 32; ++c) {
+        float2 u = __fadd2_rn(
+            make_float2(__uint_as_float(dp[2 * c]), __uint_as_float(dp[2 * c + 1])), ndlt2);
+        u = __fmul2_rn(__fmul2_rn(p[c], u), scale2);
+        dsk[c] = pack2<BF16>(u.x, u.y);
       }
-      tmem_st_x32(tDp, dsk);
+      tmem_st_x32(tS, dsk);  // over the score columns this thread has already read
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(C::kBarDsReady));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarDsReady));
     }
     if (ok && wg == 0 && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
       tc_fence_after();

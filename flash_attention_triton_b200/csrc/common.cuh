@@ -55,7 +55,7 @@ cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensor
                        const CUtensorMap& tv, const CUtensorMap& to, float* lse, int* status,
                        cudaStream_t stream);
 
-// rowstats[bh][t][0][r] = lse * log2(e) (+inf for padded rows), rowstats[bh][t][1][r] = delta.
+// rowstats[bh][t][0][r] = -lse * log2(e) (-inf for padded rows), rowstats[bh][t][1][r] = -delta.
 cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const void* dout,
                                   const float* lse, float* rowstats, cudaStream_t stream);
 

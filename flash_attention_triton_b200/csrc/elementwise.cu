@@ -47,7 +47,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 // A group of D/8 adjacent lanes owns one row: each lane reads one 16-byte piece of o and of
 // dout, multiplies, and the group reduces with shuffles in a fixed order (deterministic).
 // Rows are enumerated over the padded range [BH][T*128] so that the padding of rowstats is
-// written too (lse2 = +inf makes every probability of a padded row exactly 0 downstream).
+// written too (-lse2 = -inf makes every probability of a padded row exactly 0 downstream).
+// Both vectors are stored NEGATED so the consumers can use them as FMA / ADD addends directly.
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kPreThreads)
     bwd_preprocess_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dout,
@@ -87,8 +88,8 @@ __global__ void __launch_bounds__(kPreThreads)
       const long long tile = prow >> 7;
       const int r = static_cast<int>(prow & 127);
       const bool valid = src_row[i] >= 0;
-      rowstats[tile * 256 + r] = valid ? lse[src_row[i]] * kLog2e : INFINITY;
-      rowstats[tile * 256 + 128 + r] = valid ? acc : 0.f;
+      rowstats[tile * 256 + r] = valid ? -lse[src_row[i]] * kLog2e : -INFINITY;
+      rowstats[tile * 256 + 128 + r] = valid ? -acc : 0.f;
     }
   }
 }

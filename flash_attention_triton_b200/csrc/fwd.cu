@@ -7,18 +7,20 @@
 //   warps 4-7  softmax for Q tile 1
 //   warp  8    MMA issue (one elected thread): S_i = Q_i K_j^T, O_i += P_i V_j
 //   warp  9    TMA producer: Q once, then a K ring and a V ring
+//   warps 10-11 idle; with warps 8-9 they give registers to the softmax groups (setmaxnreg)
 // While one softmax group turns S_i into P_i the tensor cores run the other tile's MMAs.
 // S, P and O live in tensor memory; P overwrites S in place as 16-bit pairs.  The online
 // softmax works in the exp2 domain with the scale folded in, and rescales O only when the
 // running maximum has moved by more than 2^8 ("lazy rescale"); masking code runs on the
 // diagonal tile only.
 #include "common.cuh"
+#include "mma_issue.cuh"
 #include "ptx.cuh"
 
 namespace fa2 {
 namespace {
 
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;  // warps 10, 11 idle: register donors for the softmax groups
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(C::kBarSFull + i), 1);
-      mbar_init(bar(C::kBarPFull + i), 128);
+      mbar_init(bar(C::kBarPFull + i), 4);
       mbar_init(bar(C::kBarOFull + i), 1);
     }
     *abort_flag = 0;
@@ -119,6 +121,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   const uint32_t tmem_base = *tmem_slot;
   const WaitCtx w{abort_flag, status};
 
+  if (warp >= 8) {
+    reg_dec<72>();  // whole warpgroup (warps 8-11) gives registers to the softmax groups
   if (warp == 9) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -149,32 +153,16 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   } else if (warp == 8) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc(128, 128, BF16, false, false);
-      constexpr uint32_t idesc_pv = make_idesc(128, D, BF16, false, true);
-      // S_i = Q_i K^T : both operands K-major (row = q / kv index, contiguous head dim).
+      // S_i = Q_i K^T (both K-major); O_i += P_i V with P_i from tensor memory (16-bit
+      // pairs over the first 64 columns of S_i) and V as the MN-major B operand.
       auto issue_s = [&](int i, int kstage) {
-        const uint32_t qa = smem_base + C::kOffQ + i * T::kTileBytes;
-        const uint32_t ka = smem_base + C::kOffK + kstage * T::kTileBytes;
-#pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off =
-              (k / T::kKStepsPerChunk) * T::kChunkTileBytes + (k % T::kKStepsPerChunk) * 32;
-          mma_ss(tmem_base + C::kColS + i * 128,
-                 make_smem_desc(qa + off, 16, T::kAtomBytes, T::kSwizzleMode),
-                 make_smem_desc(ka + off, 16, T::kAtomBytes, T::kSwizzleMode), idesc_s, k > 0);
-        }
+        issue_rows_x_rows<D, BF16>(tmem_base + C::kColS + i * 128,
+                                   smem_base + C::kOffQ + i * T::kTileBytes,
+                                   smem_base + C::kOffK + kstage * T::kTileBytes);
       };
-      // O_i += P_i V : A = P_i from tensor memory (16-bit pairs), B = V is MN-major (the N
-      // index, head dim, is the contiguous one); 16 kv rows per MMA.
       auto issue_pv = [&](int i, int vstage, bool accumulate) {
-        const uint32_t va = smem_base + C::kOffV + vstage * T::kTileBytes;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          mma_ts(tmem_base + C::kColO + i * D, tmem_base + C::kColS + i * 128 + k * 8,
-                 make_smem_desc(va + k * 2 * T::kAtomBytes, T::kChunkTileBytes, T::kAtomBytes,
-                                T::kSwizzleMode),
-                 idesc_pv, (accumulate || k > 0) ? 1u : 0u);
-        }
+        issue_tmem_x_tile<D, BF16>(tmem_base + C::kColO + i * D, tmem_base + C::kColS + i * 128, 32,
+                                   smem_base + C::kOffV + vstage * T::kTileBytes, accumulate);
       };
       bool ok = mbar_wait(bar(C::kBarQFull), 0, w, kSiteMmaQ) &&
                 mbar_wait(bar(C::kBarKFull + 0), 0, w, kSiteMmaK);
@@ -213,8 +201,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       }
     }
     __syncwarp();
+  }
   } else {
     // ------------------------------------------------------------------ softmax groups
+    reg_inc<208>();
     const int wg = warp >> 2;
     const int qt = wg == 0 ? qt0 : qt1;
     const int nj = wg == 0 ? n0 : n1;
@@ -238,15 +228,15 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 #pragma unroll
         for (int c = 0; c < 128; ++c) s[c] = (c <= r) ? s[c] : -INFINITY;
       }
-      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+      float mx[4];
 #pragma unroll
-      for (int c = 4; c < 128; c += 4) {
-        mx0 = fmaxf(mx0, s[c]);
-        mx1 = fmaxf(mx1, s[c + 1]);
-        mx2 = fmaxf(mx2, s[c + 2]);
-        mx3 = fmaxf(mx3, s[c + 3]);
+      for (int q4 = 0; q4 < 4; ++q4) {
+        mx[q4] = max3(s[32 * q4], s[32 * q4 + 1], s[32 * q4 + 2]);
+#pragma unroll
+        for (int c = 3; c < 31; c += 2) mx[q4] = max3(mx[q4], s[32 * q4 + c], s[32 * q4 + c + 1]);
+        mx[q4] = fmaxf(mx[q4], s[32 * q4 + 31]);
       }
-      const float m_new = fmaxf(m_run, fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)));
+      const float m_new = fmaxf(max3(m_run, mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       const bool need = (m_new - m_run) * scale_log2 > kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
         const float alpha = ex2((m_run - m_new) * scale_log2);
@@ -264,25 +254,29 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
           }
         }
       }
-      const float mc = m_run * scale_log2;
-      float l0 = 0.f, l1 = 0.f;
+      // p = 2^(s*c - m*c) with packed fp32x2 FMAs; row sum in four independent packed chains.
+      const float2 sc2 = make_float2(scale_log2, scale_log2);
+      const float2 nm2 = make_float2(-m_run * scale_log2, -m_run * scale_log2);
+      float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t pk[32];
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          const float p0 = ex2(fmaf(s[64 * h + 2 * c], scale_log2, -mc));
-          const float p1 = ex2(fmaf(s[64 * h + 2 * c + 1], scale_log2, -mc));
-          l0 += p0;
-          l1 += p1;
-          pk[c] = pack2<BF16>(p0, p1);
+          float2 t = __ffma2_rn(make_float2(s[64 * h + 2 * c], s[64 * h + 2 * c + 1]), sc2, nm2);
+          t.x = ex2(t.x);
+          t.y = ex2(t.y);
+          acc[c & 3] = __fadd2_rn(acc[c & 3], t);
+          pk[c] = pack2<BF16>(t.x, t.y);
         }
         tmem_st_x32(tS + 32 * h, pk);
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(bar(C::kBarPFull + wg));
-      l_run += l0 + l1;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarPFull + wg));
+      const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
+      l_run += (a01.x + a01.y) + (a23.x + a23.y);
     }
     if (ok && nj > 0 && mbar_wait_warp(bar(C::kBarOFull + wg), 0, w, kSiteSoftO)) {
       tc_fence_after();

@@ -53,8 +53,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Returns false when the wait was abandoned (CTA abort).  `site` identifies the caller in
 // the status word.
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w,
-                                            int site) {
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, const WaitCtx& w,
+                                               int site) {
   const long long t0 = clock64();
   uint32_t it = 0;
   for (;;) {
@@ -257,6 +257,19 @@ __device__ __forceinline__ float lg2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 // Two fp32 -> one 32-bit word holding two 16-bit values, `lo` in bits [0,16).
 template <bool BF16>

@@ -65,10 +65,11 @@ int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
 
 /*
  * Backward preprocess.  Computes delta[b,h,i] = sum_d float(o[b,h,i,d]) * float(dout[b,h,i,d])
- * (replaces _backward_preprocess_do_o_dot) and stores it, together with lse * log2(e), in the
- * tile-blocked fp32 array `rowstats` that fa2_bwd consumes:
- *     rowstats[(b*H + h)][t][0][r] = lse[b,h,128*t + r] * log2(e)   (+inf for rows >= N)
- *     rowstats[(b*H + h)][t][1][r] = delta[b,h,128*t + r]           (0    for rows >= N)
+ * (replaces _backward_preprocess_do_o_dot) and stores it, together with lse * log2(e), both
+ * NEGATED (the kernels use them as FMA / ADD addends), in the tile-blocked fp32 array
+ * `rowstats` that fa2_bwd consumes:
+ *     rowstats[(b*H + h)][t][0][r] = -lse[b,h,128*t + r] * log2(e)  (-inf for rows >= N)
+ *     rowstats[(b*H + h)][t][1][r] = -delta[b,h,128*t + r]          (0    for rows >= N)
  * with t in [0, ceil(N/128)), r in [0, 128).  One 1 KiB bulk copy then stages both vectors of
  * a Q tile; the padding plays the role of the reference's seqlen_q_rounded buffers
  * (flash_attention_2.py:98-100,180).  rowstats must hold fa2_rowstats_bytes() bytes and be

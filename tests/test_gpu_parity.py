@@ -85,7 +85,7 @@ def test_forward_backward_match_oracle(shape, dtype, scale, qk_mul, det):
 
 
 def test_lse_and_rowstats_through_the_c_abi():
-    """fa2_fwd's LSE and fa2_bwd_preprocess's tile-blocked (lse*log2e, delta) array, ragged N."""
+    """fa2_fwd's LSE and fa2_bwd_preprocess's tile-blocked (-lse*log2e, -delta) array, ragged N."""
     b, h, n, d = 2, 3, 300, 64
     q, k, v, do = make_inputs((b, h, n, d), torch.bfloat16)
     ref = naive_attention(q, k, v, do)
@@ -103,8 +103,8 @@ def test_lse_and_rowstats_through_the_c_abi():
     assert _lib.device_status() == 0
     t = 3
     rs = rs.view(b * h, t, 2, 128).cpu()
-    lse2 = rs[:, :, 0].reshape(b * h, t * 128)
-    delta = rs[:, :, 1].reshape(b * h, t * 128)
+    lse2 = -rs[:, :, 0].reshape(b * h, t * 128)  # both vectors are stored negated
+    delta = -rs[:, :, 1].reshape(b * h, t * 128)
     want_delta = (o.cpu().double() * do.double()).sum(-1).reshape(b * h, n)
     assert (delta[:, :n].double() - want_delta).abs().max() < 1e-5 * max(1.0, want_delta.abs().max())
     assert (lse2[:, :n].double() - lse.cpu().double().reshape(b * h, n) * math.log2(math.e)).abs().max() < 1e-5
