@@ -145,7 +145,11 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
   using C = DkdvCfg<D, FUSE>;
   using T = Tile<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Role index: the producer / MMA group takes hardware warps 0-3 (lowest ids on their
+  // schedulers), the compute and reduction groups follow; shifts are multiples of 4, so
+  // role % 4 is still the tensor-memory lane quarter of the hardware warp.
+  constexpr int kWarps = C::kThreads / 32;
+  const int warp = ((threadIdx.x >> 5) + C::kMmaWarp) % kWarps, lane = threadIdx.x & 31;
   const uint32_t smem_base = smem_u32(smem);
   if (smem_base & 1023u) {
     if (threadIdx.x == 0) atomicCAS(status, 0, 0x20000 | kBSiteAlign);
@@ -160,6 +164,8 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
   const int jt = blockIdx.x;  // KV tile; tile 0 has the most Q tiles and is scheduled first
   const int bh = blockIdx.y;
   const int nq = ntiles - jt;  // Q tiles jt .. ntiles-1
+  const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
+  (void)traced;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(C::kBarKV), 1);
@@ -192,126 +198,157 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
 
   if (warp >= C::kMmaWarp) {
     // ---------------------------------------------------------------- producer / MMA group
-    reg_dec<64>();
-    if (warp == C::kLoadWarp && lane == 0) {
-      prefetch_tensormap(&tq);
-      prefetch_tensormap(&tk);
-      prefetch_tensormap(&tv);
-      prefetch_tensormap(&tdo);
-      mbar_arrive_expect_tx(bar(C::kBarKV), 2 * T::kTileBytes);
-      for (int ch = 0; ch < T::kChunks; ++ch) {
-        tma_load_3d(smem_base + C::kOffK + ch * T::kChunkTileBytes, &tk, ch * T::kChunkElems,
-                    jt * 128, bh, bar(C::kBarKV));
-        tma_load_3d(smem_base + C::kOffV + ch * T::kChunkTileBytes, &tv, ch * T::kChunkElems,
-                    jt * 128, bh, bar(C::kBarKV));
+    reg_dec<72>();
+    if (warp == C::kLoadWarp) {
+      // TMA producer: whole warp, converged; the elected lane arms barriers and issues copies.
+      const uint32_t elected = elect_one();
+      if (elected) {
+        prefetch_tensormap(&tq);
+        prefetch_tensormap(&tk);
+        prefetch_tensormap(&tv);
+        prefetch_tensormap(&tdo);
+        mbar_arrive_expect_tx(bar(C::kBarKV), 2 * T::kTileBytes);
+        for (int ch = 0; ch < T::kChunks; ++ch) {
+          tma_load_3d(smem_base + C::kOffK + ch * T::kChunkTileBytes, &tk, ch * T::kChunkElems,
+                      jt * 128, bh, bar(C::kBarKV));
+          tma_load_3d(smem_base + C::kOffV + ch * T::kChunkTileBytes, &tv, ch * T::kChunkElems,
+                      jt * 128, bh, bar(C::kBarKV));
+        }
       }
       for (int ii = 0; ii < nq; ++ii) {
         const int s = ii % C::kStages, ph = (ii / C::kStages) & 1;
         const int qt = jt + ii;
-        if (!mbar_wait(bar(C::kBarQEmpty + s), ph ^ 1, w, kBSiteLoadQ)) break;
-        mbar_arrive_expect_tx(bar(C::kBarQFull + s), T::kTileBytes + 1024);
-        for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffQ + s * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
-                      ch * T::kChunkElems, qt * 128, bh, bar(C::kBarQFull + s));
-        bulk_load_1d(smem_base + C::kOffStats + s * 1024,
-                     rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024,
-                     bar(C::kBarQFull + s));
-        if (!mbar_wait(bar(C::kBarDOEmpty + s), ph ^ 1, w, kBSiteLoadDO)) break;
-        mbar_arrive_expect_tx(bar(C::kBarDOFull + s), T::kTileBytes);
-        for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffDO + s * T::kTileBytes + ch * T::kChunkTileBytes, &tdo,
-                      ch * T::kChunkElems, qt * 128, bh, bar(C::kBarDOFull + s));
+        if (!mbar_wait_warp(bar(C::kBarQEmpty + s), ph ^ 1, w, kBSiteLoadQ)) break;
+        if (elected) {
+          mbar_arrive_expect_tx(bar(C::kBarQFull + s), T::kTileBytes + 1024);
+#pragma unroll
+          for (int ch = 0; ch < T::kChunks; ++ch)
+            tma_load_3d(smem_base + C::kOffQ + s * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
+                        ch * T::kChunkElems, qt * 128, bh, bar(C::kBarQFull + s));
+          bulk_load_1d(smem_base + C::kOffStats + s * 1024,
+                       rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024,
+                       bar(C::kBarQFull + s));
+        }
+        if (!mbar_wait_warp(bar(C::kBarDOEmpty + s), ph ^ 1, w, kBSiteLoadDO)) break;
+        if (elected) {
+          mbar_arrive_expect_tx(bar(C::kBarDOFull + s), T::kTileBytes);
+#pragma unroll
+          for (int ch = 0; ch < T::kChunks; ++ch)
+            tma_load_3d(smem_base + C::kOffDO + s * T::kTileBytes + ch * T::kChunkTileBytes, &tdo,
+                        ch * T::kChunkElems, qt * 128, bh, bar(C::kBarDOFull + s));
+        }
       }
-    } else if (warp == C::kMmaWarp && lane == 0) {
+    } else if (warp == C::kMmaWarp) {
+      // Whole warp, converged; only the elected lane issues MMAs and commits.
+      const uint32_t elected = elect_one();
       const uint32_t ka = smem_base + C::kOffK, va = smem_base + C::kOffV;
+      auto commit = [&](int b) {
+        if (elected) mma_commit(bar(b));
+      };
       // St / dPt: [128 kv, 128 q] = (K or V tile) x (Q or dO tile)^T, both K-major.
       auto issue_t = [&](uint32_t col, uint32_t a_base, uint32_t b_base) {
-        issue_rows_x_rows<D, BF16>(tmem_base + col, a_base, b_base);
+        issue_rows_x_rows<D, BF16>(elected, tmem_base + col, a_base, b_base);
       };
       // dV / dK: [128 kv, D] += (16-bit Pt or dSt in tensor memory) x (dO or Q tile, MN-major).
       auto issue_acc = [&](uint32_t col_d, uint32_t col_a, uint32_t b_base, bool accumulate) {
-        issue_tmem_x_tile<D, BF16>(tmem_base + col_d, tmem_base + col_a, 64, b_base, accumulate);
+        issue_tmem_x_tile<D, BF16>(elected, tmem_base + col_d, tmem_base + col_a, 64, b_base,
+                                   accumulate);
       };
-      bool ok = mbar_wait(bar(C::kBarKV), 0, w, kBSiteMmaKV) &&
-                mbar_wait(bar(C::kBarQFull + 0), 0, w, kBSiteMmaQ);
+      bool ok = mbar_wait_warp(bar(C::kBarKV), 0, w, kBSiteMmaKV) &&
+                mbar_wait_warp(bar(C::kBarQFull + 0), 0, w, kBSiteMmaQ);
       if (ok) {
         issue_t(C::kColSt, ka, smem_base + C::kOffQ);
-        mma_commit(bar(C::kBarStFull));
-        ok = mbar_wait(bar(C::kBarDOFull + 0), 0, w, kBSiteMmaDO);
+        commit(C::kBarStFull);
+        ok = mbar_wait_warp(bar(C::kBarDOFull + 0), 0, w, kBSiteMmaDO);
       }
       if (ok) {
         issue_t(C::kColDpt, va, smem_base + C::kOffDO);
-        mma_commit(bar(C::kBarDptFull));
+        commit(C::kBarDptFull);
       }
+      // Issue order inside one iteration (the tensor pipe executes in issue order, so the
+      // order decides what can overlap):
+      //   plain:  [Pt ready] dV(i), St(i+1)                 [dSt ready] dK(i), dPt(i+1)
+      //   fused:  [Pt ready] dV(i), [dQ(i-1) drained] dPt(i), St(i+1)   [dSt ready] dK(i), dQ(i)
+      // In the fused kernel dPt shares its columns with dQ, so dPt(i) has to wait for the
+      // reduction group; issuing dV(i) first keeps the pipe busy during that drain.
       for (int ii = 0; ok && ii < nq; ++ii) {
-        const int s = ii % C::kStages;
+        const int s = ii % C::kStages, ph = (ii / C::kStages) & 1;
         const int s1 = (ii + 1) % C::kStages, ph1 = ((ii + 1) / C::kStages) & 1;
         const uint32_t qa = smem_base + C::kOffQ + s * T::kTileBytes;
         const uint32_t doa = smem_base + C::kOffDO + s * T::kTileBytes;
-        if (!(ok = mbar_wait(bar(C::kBarPtReady), ii & 1, w, kBSiteMmaPt))) break;
+        if (!(ok = mbar_wait_warp(bar(C::kBarPtReady), ii & 1, w, kBSiteMmaPt))) break;
         tc_fence_after();
+        FA2_TRACE_EVENT(traced && elected, ii * 16 + 0);
         issue_acc(C::kColDV, C::kColSt, doa, ii > 0);  // dV += Pt dO_i
-        mma_commit(bar(C::kBarDOEmpty + s));
-        if (ii + 1 < nq) {
-          if (!(ok = mbar_wait(bar(C::kBarQFull + s1), ph1, w, kBSiteMmaQ))) break;
-          issue_t(C::kColSt, ka, smem_base + C::kOffQ + s1 * T::kTileBytes);  // St(i+1)
-          mma_commit(bar(C::kBarStFull));
+        if constexpr (FUSE) {
+          if (ii > 0) {
+            if (!(ok = mbar_wait_warp(bar(C::kBarDqDrained), (ii - 1) & 1, w, kBSiteMmaDrain))) break;
+            tc_fence_after();
+            FA2_TRACE_EVENT(traced && elected, ii * 16 + 4);
+            if (!(ok = mbar_wait_warp(bar(C::kBarDOFull + s), ph, w, kBSiteMmaDO))) break;
+            issue_t(C::kColDpt, va, doa);  // dPt(i)
+            commit(C::kBarDptFull);
+            FA2_TRACE_EVENT(traced && elected, ii * 16 + 5);
+          }
         }
-        if (!(ok = mbar_wait(bar(C::kBarDsReady), ii & 1, w, kBSiteMmaDs))) break;
+        commit(C::kBarDOEmpty + s);
+        if (ii + 1 < nq) {
+          if (!(ok = mbar_wait_warp(bar(C::kBarQFull + s1), ph1, w, kBSiteMmaQ))) break;
+          issue_t(C::kColSt, ka, smem_base + C::kOffQ + s1 * T::kTileBytes);  // St(i+1)
+          commit(C::kBarStFull);
+        }
+        FA2_TRACE_EVENT(traced && elected, ii * 16 + 1);
+        if (!(ok = mbar_wait_warp(bar(C::kBarDsReady), ii & 1, w, kBSiteMmaDs))) break;
         tc_fence_after();
+        FA2_TRACE_EVENT(traced && elected, ii * 16 + 2);
         issue_acc(C::kColDK, C::kColDpt, qa, ii > 0);  // dK += dSt Q_i
-        mma_commit(bar(C::kBarQEmpty + s));
+        commit(C::kBarQEmpty + s);
         if constexpr (FUSE) {
           // dQ_i[128 q, D] = dS[q, kv] * K[kv, d]: A = dS^T tile in smem (q contiguous ->
           // MN-major), B = K tile (d contiguous -> MN-major); 16 kv rows per MMA.
-          issue_tileT_x_tile<D, BF16>(tmem_base + C::kColDpt, smem_base + C::kOffDS, ka);
-          mma_commit(bar(C::kBarDqFull));
-        }
-        if (ii + 1 < nq) {
-          if constexpr (FUSE) {
-            if (!(ok = mbar_wait(bar(C::kBarDqDrained), ii & 1, w, kBSiteMmaDrain))) break;
-            tc_fence_after();
-          }
-          if (!(ok = mbar_wait(bar(C::kBarDOFull + s1), ph1, w, kBSiteMmaDO))) break;
+          issue_tileT_x_tile<D, BF16>(elected, tmem_base + C::kColDpt, smem_base + C::kOffDS, ka);
+          commit(C::kBarDqFull);
+        } else if (ii + 1 < nq) {
+          if (!(ok = mbar_wait_warp(bar(C::kBarDOFull + s1), ph1, w, kBSiteMmaDO))) break;
           issue_t(C::kColDpt, va, smem_base + C::kOffDO + s1 * T::kTileBytes);  // dPt(i+1)
-          mma_commit(bar(C::kBarDptFull));
+          commit(C::kBarDptFull);
         }
+        FA2_TRACE_EVENT(traced && elected, ii * 16 + 3);
       }
-      if (ok) mma_commit(bar(C::kBarDone));
+      if (ok) commit(C::kBarDone);
     }
     __syncwarp();
   } else if (FUSE && warp >= 8) {
     // ---------------------------------------------------------------- dQ reduction group
-    reg_dec<104>();
+    reg_inc<136>();  // 512-thread kernel starts at 128 registers per thread
     const int w4 = warp & 3;
     const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
     for (int ii = 0; ii < nq; ++ii) {
       if (!mbar_wait_warp(bar(C::kBarDqFull), ii & 1, w, kBSiteRedDq)) break;
       tc_fence_after();
+      FA2_TRACE_EVENT(traced && warp == 8 && lane == 0, ii * 16 + 11);
       const int qt = jt + ii;
       float* dst = dq_accum + (((static_cast<size_t>(bh) * ntiles + qt) * 4 + w4) * (D / 4)) * 128 +
                    lane * 4;
+      // Whole dQ tile into registers first, so the MMA warp can reuse the columns at once;
+      // the atomics follow at leisure.
+      uint32_t v[D];
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 64) {
-        uint32_t v[64];
-        tmem_ld_x32(tmem_base + lane_base + C::kColDpt + c0, v);
-        if (D > 32) tmem_ld_x32(tmem_base + lane_base + C::kColDpt + c0 + 32, v + 32);
-        tmem_wait_ld();
-        if (c0 + 64 >= D) {  // whole tile is in registers: the MMA warp may overwrite it
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(bar(C::kBarDqDrained));
-        }
+      for (int c0 = 0; c0 < D; c0 += 32) tmem_ld_x32(tmem_base + lane_base + C::kColDpt + c0, v + c0);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarDqDrained));
+      FA2_TRACE_EVENT(traced && warp == 8 && lane == 0, ii * 16 + 12);
 #pragma unroll
-        for (int k = 0; k < (D > 32 ? 16 : 8); ++k)
-          red_add_v4(dst + (c0 / 4 + k) * 128, __uint_as_float(v[4 * k]),
-                     __uint_as_float(v[4 * k + 1]), __uint_as_float(v[4 * k + 2]),
-                     __uint_as_float(v[4 * k + 3]));
-      }
+      for (int k = 0; k < D / 4; ++k)
+        red_add_v4(dst + k * 128, __uint_as_float(v[4 * k]), __uint_as_float(v[4 * k + 1]),
+                   __uint_as_float(v[4 * k + 2]), __uint_as_float(v[4 * k + 3]));
+      FA2_TRACE_EVENT(traced && warp == 8 && lane == 0, ii * 16 + 13);
     }
   } else {
     // ---------------------------------------------------------------- compute groups
-    if constexpr (FUSE) reg_inc<168>(); else reg_inc<208>();
+    if constexpr (FUSE) reg_inc<152>(); else reg_inc<208>();
     const int wg = warp >> 2;  // 0: score columns (q) 0..63, 1: 64..127
     const int w4 = warp & 3;
     const int r = w4 * 32 + lane;  // kv row in the tile = tensor-memory lane
@@ -329,12 +366,14 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
       if (!(ok = mbar_wait_warp(bar(C::kBarQFull + s), ph, w, kBSiteCmpQ))) break;
       if (!(ok = mbar_wait_warp(bar(C::kBarStFull), ii & 1, w, kBSiteCmpSt))) break;
       tc_fence_after();
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 6);
       float2 p[32];  // P^T for this thread's kv row, q columns wg*64 .. wg*64+63
       {
         uint32_t sr[64];
         tmem_ld_x32(tSt, sr);
         tmem_ld_x32(tSt + 32, sr + 32);
         tmem_wait_ld();
+        FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 7);
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 l = nlse[c4];
@@ -363,9 +402,11 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarPtReady));
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 8);
 
       if (!(ok = mbar_wait_warp(bar(C::kBarDptFull), ii & 1, w, kBSiteCmpDpt))) break;
       tc_fence_after();
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 9);
       uint32_t dsk[32];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -399,6 +440,7 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarDsReady));
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 10);
     }
     // epilogue: group 0 stores dV, group 1 stores dK, staged through the idle dO / Q buffers
     if (ok && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
@@ -470,7 +512,8 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
   using C = DqCfg<D>;
   using T = Tile<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Role index: producer / MMA group on hardware warps 0-3, compute groups on 4-11.
+  const int warp = ((threadIdx.x >> 5) + C::kMmaWarp) % (C::kThreads / 32), lane = threadIdx.x & 31;
   const uint32_t smem_base = smem_u32(smem);
   if (smem_base & 1023u) {
     if (threadIdx.x == 0) atomicCAS(status, 0, 0x20000 | kBSiteAlign);
@@ -485,6 +528,8 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
   const int qt = ntiles - 1 - static_cast<int>(blockIdx.x);  // heaviest Q tile first
   const int bh = blockIdx.y;
   const int nkv = qt + 1;
+  const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
+  (void)traced;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(C::kBarQ), 1);
@@ -518,55 +563,70 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
 
   if (warp >= C::kMmaWarp) {
     reg_dec<72>();
-    if (warp == C::kLoadWarp && lane == 0) {
-      prefetch_tensormap(&tq);
-      prefetch_tensormap(&tk);
-      prefetch_tensormap(&tv);
-      prefetch_tensormap(&tdo);
-      mbar_arrive_expect_tx(bar(C::kBarQ), 2 * T::kTileBytes + 1024);
-      for (int ch = 0; ch < T::kChunks; ++ch) {
-        tma_load_3d(smem_base + C::kOffQ + ch * T::kChunkTileBytes, &tq, ch * T::kChunkElems,
-                    qt * 128, bh, bar(C::kBarQ));
-        tma_load_3d(smem_base + C::kOffDO + ch * T::kChunkTileBytes, &tdo, ch * T::kChunkElems,
-                    qt * 128, bh, bar(C::kBarQ));
+    if (warp == C::kLoadWarp) {
+      // TMA producer: whole warp, converged; the elected lane arms barriers and issues copies.
+      const uint32_t elected = elect_one();
+      if (elected) {
+        prefetch_tensormap(&tq);
+        prefetch_tensormap(&tk);
+        prefetch_tensormap(&tv);
+        prefetch_tensormap(&tdo);
+        mbar_arrive_expect_tx(bar(C::kBarQ), 2 * T::kTileBytes + 1024);
+        for (int ch = 0; ch < T::kChunks; ++ch) {
+          tma_load_3d(smem_base + C::kOffQ + ch * T::kChunkTileBytes, &tq, ch * T::kChunkElems,
+                      qt * 128, bh, bar(C::kBarQ));
+          tma_load_3d(smem_base + C::kOffDO + ch * T::kChunkTileBytes, &tdo, ch * T::kChunkElems,
+                      qt * 128, bh, bar(C::kBarQ));
+        }
+        bulk_load_1d(smem_base + C::kOffStats,
+                     rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024, bar(C::kBarQ));
       }
-      bulk_load_1d(smem_base + C::kOffStats,
-                   rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024, bar(C::kBarQ));
       for (int j = 0; j < nkv; ++j) {
         const int ks = j % C::kKStages, kph = (j / C::kKStages) & 1;
-        if (!mbar_wait(bar(C::kBarKEmpty + ks), kph ^ 1, w, kBSiteLoadQ)) break;
-        mbar_arrive_expect_tx(bar(C::kBarKFull + ks), T::kTileBytes);
-        for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
-                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + ks));
+        if (!mbar_wait_warp(bar(C::kBarKEmpty + ks), kph ^ 1, w, kBSiteLoadQ)) break;
+        if (elected) {
+          mbar_arrive_expect_tx(bar(C::kBarKFull + ks), T::kTileBytes);
+#pragma unroll
+          for (int ch = 0; ch < T::kChunks; ++ch)
+            tma_load_3d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
+                        ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + ks));
+        }
         const int vs = j % C::kVStages, vph = (j / C::kVStages) & 1;
-        if (!mbar_wait(bar(C::kBarVEmpty + vs), vph ^ 1, w, kBSiteLoadDO)) break;
-        mbar_arrive_expect_tx(bar(C::kBarVFull + vs), T::kTileBytes);
-        for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
-                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarVFull + vs));
+        if (!mbar_wait_warp(bar(C::kBarVEmpty + vs), vph ^ 1, w, kBSiteLoadDO)) break;
+        if (elected) {
+          mbar_arrive_expect_tx(bar(C::kBarVFull + vs), T::kTileBytes);
+#pragma unroll
+          for (int ch = 0; ch < T::kChunks; ++ch)
+            tma_load_3d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
+                        ch * T::kChunkElems, j * 128, bh, bar(C::kBarVFull + vs));
+        }
       }
-    } else if (warp == C::kMmaWarp && lane == 0) {
+    } else if (warp == C::kMmaWarp) {
+      // Whole warp, converged; only the elected lane issues MMAs and commits.
+      const uint32_t elected = elect_one();
+      auto commit = [&](int b) {
+        if (elected) mma_commit(bar(b));
+      };
       const uint32_t qa = smem_base + C::kOffQ, doa = smem_base + C::kOffDO;
       auto k_addr = [&](int j) { return smem_base + C::kOffK + (j % C::kKStages) * T::kTileBytes; };
       auto k_wait = [&](int j) {
-        return mbar_wait(bar(C::kBarKFull + j % C::kKStages), (j / C::kKStages) & 1, w, kBSiteMmaKV);
+        return mbar_wait_warp(bar(C::kBarKFull + j % C::kKStages), (j / C::kKStages) & 1, w, kBSiteMmaKV);
       };
       auto issue_s = [&](int j) {  // S(j) -> score buffer j%2
-        issue_rows_x_rows<D, BF16>(tmem_base + C::kColS + (j & 1) * 128, qa, k_addr(j));
-        mma_commit(bar(C::kBarSFull + (j & 1)));
+        issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS + (j & 1) * 128, qa, k_addr(j));
+        commit(C::kBarSFull + (j & 1));
       };
       auto issue_dp = [&](int j) {  // dP(j); V_j is free afterwards
         const int vs = j % C::kVStages;
-        issue_rows_x_rows<D, BF16>(tmem_base + C::kColDp, doa,
+        issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColDp, doa,
                                    smem_base + C::kOffV + vs * T::kTileBytes);
-        mma_commit(bar(C::kBarDpFull));
-        mma_commit(bar(C::kBarVEmpty + vs));
+        commit(C::kBarDpFull);
+        commit(C::kBarVEmpty + vs);
       };
       auto v_wait = [&](int j) {
-        return mbar_wait(bar(C::kBarVFull + j % C::kVStages), (j / C::kVStages) & 1, w, kBSiteMmaDO);
+        return mbar_wait_warp(bar(C::kBarVFull + j % C::kVStages), (j / C::kVStages) & 1, w, kBSiteMmaDO);
       };
-      bool ok = mbar_wait(bar(C::kBarQ), 0, w, kBSiteMmaQ) && k_wait(0);
+      bool ok = mbar_wait_warp(bar(C::kBarQ), 0, w, kBSiteMmaQ) && k_wait(0);
       if (ok) {
         issue_s(0);
         ok = v_wait(0);
@@ -578,23 +638,28 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
       for (int j = 0; ok && j < nkv; ++j) {
         if (j + 1 < nkv) {
           // dP columns are free once every compute warp has read dP(j)
-          if (!(ok = mbar_wait(bar(C::kBarDpConsumed), j & 1, w, kBSiteMmaDrain))) break;
+          if (!(ok = mbar_wait_warp(bar(C::kBarDpConsumed), j & 1, w, kBSiteMmaDrain))) break;
           tc_fence_after();
+          FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 0);
           if (!(ok = v_wait(j + 1))) break;
           issue_dp(j + 1);
+          FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 1);
         }
-        if (!(ok = mbar_wait(bar(C::kBarDsReady), j & 1, w, kBSiteMmaDs))) break;
+        if (!(ok = mbar_wait_warp(bar(C::kBarDsReady), j & 1, w, kBSiteMmaDs))) break;
         tc_fence_after();
+        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 2);
         // dQ += dS(j) K_j : A = 16-bit dS over score buffer j%2, B = K_j as MN-major tile
-        issue_tmem_x_tile<D, BF16>(tmem_base + C::kColDQ, tmem_base + C::kColS + (j & 1) * 128, 64,
+        issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDQ, tmem_base + C::kColS + (j & 1) * 128, 64,
                                    k_addr(j), j > 0);
-        mma_commit(bar(C::kBarKEmpty + j % C::kKStages));
+        commit(C::kBarKEmpty + j % C::kKStages);
+        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 3);
         if (j + 2 < nkv) {
           if (!(ok = k_wait(j + 2))) break;
           issue_s(j + 2);  // reuses buffer j%2; ordered after dQ(j) by the in-order MMA pipe
+          FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 4);
         }
       }
-      if (ok) mma_commit(bar(C::kBarDone));
+      if (ok) commit(C::kBarDone);
     }
     __syncwarp();
   } else {
@@ -617,6 +682,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
       const uint32_t tS = tmem_base + lane_base + C::kColS + (j & 1) * 128 + wg * 64;
       if (!(ok = mbar_wait_warp(bar(C::kBarSFull + (j & 1)), (j >> 1) & 1, w, kBSiteCmpSt))) break;
       tc_fence_after();
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 6);
       float2 p[32];
       {
         uint32_t sr[64];
@@ -637,8 +703,10 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
           p[c].y = (wg * 64 + 2 * c + 1 <= r) ? p[c].y : 0.f;
         }
       }
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 7);
       if (!(ok = mbar_wait_warp(bar(C::kBarDpFull), j & 1, w, kBSiteCmpDpt))) break;
       tc_fence_after();
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 8);
       uint32_t dp[64];
       tmem_ld_x32(tDp, dp);
       tmem_ld_x32(tDp + 32, dp + 32);
@@ -646,6 +714,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarDpConsumed));
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 9);
       uint32_t dsk[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
@@ -659,6 +728,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarDsReady));
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 10);
     }
     if (ok && wg == 0 && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
       tc_fence_after();
@@ -710,6 +780,12 @@ cudaError_t launch_dq_t(const AttnShape& s, const CUtensorMap& tq, const CUtenso
 }
 
 }  // namespace
+
+#ifdef FA2_TRACE
+extern "C" int fa2_trace_read_bwd(long long* out, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n));
+}
+#endif
 
 cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                             const CUtensorMap& tv, const CUtensorMap& tdo,

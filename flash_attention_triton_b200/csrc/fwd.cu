@@ -3,32 +3,45 @@
 // Replaces _forward_kernel (src/flash_attention_triton/_triton_kernels_v2.py:11-189 of the
 // reference).  One CTA owns two adjacent 128-row Q tiles of one (batch, head) and walks the KV
 // tiles 0..diagonal.  Warp roles:
-//   warps 0-3  softmax for Q tile 0   (thread = one score row = one tensor-memory lane)
-//   warps 4-7  softmax for Q tile 1
-//   warp  8    MMA issue (one elected thread): S_i = Q_i K_j^T, O_i += P_i V_j
-//   warp  9    TMA producer: Q once, then a K ring and a V ring
+//   warps 0-3   softmax for Q tile 0   (thread = one score row = one tensor-memory lane)
+//   warps 4-7   softmax for Q tile 1
+//   warp  8     MMA issue (one elected thread): S = Q_i K_j^T, O_i += P_i V_j
+//   warp  9     TMA producer: Q once, then a K ring and a V ring
 //   warps 10-11 idle; with warps 8-9 they give registers to the softmax groups (setmaxnreg)
-// While one softmax group turns S_i into P_i the tensor cores run the other tile's MMAs.
-// S, P and O live in tensor memory; P overwrites S in place as 16-bit pairs.  The online
-// softmax works in the exp2 domain with the scale folded in, and rescales O only when the
-// running maximum has moved by more than 2^8 ("lazy rescale"); masking code runs on the
-// diagonal tile only.
+//
+// Tensor memory: ONE score buffer S shared by both Q tiles, a 16-bit probability buffer P_i per
+// tile and an output accumulator O_i per tile.  A softmax group copies its score row into
+// registers as soon as S is complete and hands the buffer back at once, so the next S product
+// (for the other tile) runs while the group is still exponentiating; because P_i has its own
+// columns, S_i(j+1) does not wait for O_i += P_i(j) V_j either.  Neither softmax group ever
+// waits for its own MMAs in steady state: the tensor pipe sees four tile products per KV step
+// back to back.
+//
+// The online softmax works in the exp2 domain with the scale folded in, and rescales O only
+// when the running maximum has moved by more than 2^8 ("lazy rescale"); masking code runs on
+// the diagonal tile only.  A fixed fraction of the exponentials is evaluated with a
+// polynomial on the FMA pipe because the MUFU rate (16 / clk / SM) would otherwise bound the
+// kernel: 2 x 128 x 128 exponentials per KV step cost as many cycles as the four MMAs.
 #include "common.cuh"
 #include "mma_issue.cuh"
 #include "ptx.cuh"
 
+#ifndef FA2_FWD_POLY_PAIRS_PER_8
+#define FA2_FWD_POLY_PAIRS_PER_8 3  // of every 8 column pairs, this many use ex2_poly2
+#endif
+
 namespace fa2 {
 namespace {
 
-constexpr int kFwdThreads = 384;  // warps 10, 11 idle: register donors for the softmax groups
+constexpr int kFwdThreads = 384;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 constexpr float kLn2 = 0.6931471805599453f;
 
 template <int D>
 struct FwdCfg {
   using T = Tile<D>;
-  static constexpr int kKStages = D == 128 ? 2 : (D == 64 ? 3 : 4);
-  static constexpr int kVStages = kKStages;
+  static constexpr int kKStages = D == 128 ? 3 : 4;
+  static constexpr int kVStages = D == 128 ? 2 : 4;
   static constexpr int kOffQ = 0;
   static constexpr int kOffK = kOffQ + 2 * T::kTileBytes;
   static constexpr int kOffV = kOffK + kKStages * T::kTileBytes;
@@ -39,13 +52,15 @@ struct FwdCfg {
   static constexpr int kBarKEmpty = kBarKFull + kKStages;
   static constexpr int kBarVFull = kBarKEmpty + kKStages;
   static constexpr int kBarVEmpty = kBarVFull + kVStages;
-  static constexpr int kBarSFull = kBarVEmpty + kVStages;  // 2
-  static constexpr int kBarPFull = kBarSFull + 2;          // 2
-  static constexpr int kBarOFull = kBarPFull + 2;          // 2
-  static constexpr int kNumBars = kBarOFull + 2;
+  static constexpr int kBarSFull = kBarVEmpty + kVStages;  // 2: S holds tile i's scores
+  static constexpr int kBarSFree = kBarSFull + 2;    // 2: group i has copied S out (4 arrivals)
+  static constexpr int kBarPFull = kBarSFree + 2;    // 2: P_i written, O_i rescaled (4 arrivals)
+  static constexpr int kBarPvDone = kBarPFull + 2;   // 2: O_i += P_i V completed
+  static constexpr int kNumBars = kBarPvDone + 2;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
   // tensor-memory columns
-  static constexpr int kColS = 0;    // S0 at 0, S1 at 128 (P_i aliases the first 64 of S_i)
+  static constexpr int kColS = 0;
+  static constexpr int kColP = 128;  // P0 at 128, P1 at 192 (64 columns of 16-bit pairs each)
   static constexpr int kColO = 256;  // O0 at 256, O1 at 256 + D
   static constexpr int kTmemCols = 512;
 };
@@ -57,7 +72,9 @@ enum FwdSite {
   kSiteMmaK,
   kSiteMmaV,
   kSiteMmaP,
+  kSiteMmaSFree,
   kSiteSoftS,
+  kSiteSoftPv,
   kSiteSoftO,
   kSiteAlign
 };
@@ -71,7 +88,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   using T = Tile<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
 
-  const int warp = threadIdx.x >> 5;
+  // Role index: hardware warps 0-3 take roles 8-11 (MMA, TMA, idle, idle) and hardware warps
+  // 4-11 the softmax roles 0-7, so the latency-critical MMA / TMA warps have the lowest
+  // hardware warp ids on their schedulers.  The shift is a multiple of 4, so role % 4 is
+  // still the tensor-memory lane quarter the hardware warp may access.
+  const int warp = ((threadIdx.x >> 5) + 8) % 12;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = smem_u32(smem);
   if (smem_base & 1023u) {  // swizzled tiles need 1024-byte alignment
@@ -88,9 +109,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   const int bh = blockIdx.y;
   const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
   const bool has1 = qt1 < ntiles;
-  const int n0 = qt0 + 1;
-  const int n1 = has1 ? qt1 + 1 : 0;
+  const int n0 = qt0 + 1;             // KV tiles of Q tile 0
+  const int n1 = has1 ? qt1 + 1 : 0;  // KV tiles of Q tile 1 (one more than tile 0)
   const int nkv = has1 ? n1 : n0;
+  const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
+  (void)traced;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(C::kBarQFull), 1);
@@ -104,8 +127,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(bar(C::kBarSFull + i), 1);
+      mbar_init(bar(C::kBarSFree + i), 4);
       mbar_init(bar(C::kBarPFull + i), 4);
-      mbar_init(bar(C::kBarOFull + i), 1);
+      mbar_init(bar(C::kBarPvDone + i), 1);
     }
     *abort_flag = 0;
     fence_mbar_init();
@@ -123,85 +147,104 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 
   if (warp >= 8) {
     reg_dec<72>();  // whole warpgroup (warps 8-11) gives registers to the softmax groups
-  if (warp == 9) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      prefetch_tensormap(&tq);
-      prefetch_tensormap(&tk);
-      prefetch_tensormap(&tv);
-      mbar_arrive_expect_tx(bar(C::kBarQFull), (has1 ? 2 : 1) * T::kTileBytes);
-      for (int i = 0; i < (has1 ? 2 : 1); ++i)
-        for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffQ + i * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
-                      ch * T::kChunkElems, (qt0 + i) * 128, bh, bar(C::kBarQFull));
-      for (int j = 0; j < nkv; ++j) {
-        const int ks = j % C::kKStages, kph = (j / C::kKStages) & 1;
-        if (!mbar_wait(bar(C::kBarKEmpty + ks), kph ^ 1, w, kSiteLoadK)) break;
-        mbar_arrive_expect_tx(bar(C::kBarKFull + ks), T::kTileBytes);
-        for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
-                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + ks));
-        const int vs = j % C::kVStages, vph = (j / C::kVStages) & 1;
-        if (!mbar_wait(bar(C::kBarVEmpty + vs), vph ^ 1, w, kSiteLoadV)) break;
-        mbar_arrive_expect_tx(bar(C::kBarVFull + vs), T::kTileBytes);
-        for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_3d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
-                      ch * T::kChunkElems, j * 128, bh, bar(C::kBarVFull + vs));
+    if (warp == 9) {
+      // ---------------------------------------------------------------- TMA producer
+      // (whole warp, converged; only the elected lane arms barriers and issues copies)
+      const uint32_t elected = elect_one();
+      if (elected) {
+        prefetch_tensormap(&tq);
+        prefetch_tensormap(&tk);
+        prefetch_tensormap(&tv);
+        mbar_arrive_expect_tx(bar(C::kBarQFull), (has1 ? 2 : 1) * T::kTileBytes);
+        for (int i = 0; i < (has1 ? 2 : 1); ++i)
+          for (int ch = 0; ch < T::kChunks; ++ch)
+            tma_load_3d(smem_base + C::kOffQ + i * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
+                        ch * T::kChunkElems, (qt0 + i) * 128, bh, bar(C::kBarQFull));
       }
-    }
-    __syncwarp();
-  } else if (warp == 8) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      // S_i = Q_i K^T (both K-major); O_i += P_i V with P_i from tensor memory (16-bit
-      // pairs over the first 64 columns of S_i) and V as the MN-major B operand.
-      auto issue_s = [&](int i, int kstage) {
-        issue_rows_x_rows<D, BF16>(tmem_base + C::kColS + i * 128,
-                                   smem_base + C::kOffQ + i * T::kTileBytes,
-                                   smem_base + C::kOffK + kstage * T::kTileBytes);
-      };
-      auto issue_pv = [&](int i, int vstage, bool accumulate) {
-        issue_tmem_x_tile<D, BF16>(tmem_base + C::kColO + i * D, tmem_base + C::kColS + i * 128, 32,
-                                   smem_base + C::kOffV + vstage * T::kTileBytes, accumulate);
-      };
-      bool ok = mbar_wait(bar(C::kBarQFull), 0, w, kSiteMmaQ) &&
-                mbar_wait(bar(C::kBarKFull + 0), 0, w, kSiteMmaK);
-      if (ok) {
-        issue_s(0, 0);
-        mma_commit(bar(C::kBarSFull + 0));
-        if (has1) {
-          issue_s(1, 0);
-          mma_commit(bar(C::kBarSFull + 1));
-        }
-        mma_commit(bar(C::kBarKEmpty + 0));
-      }
-      for (int j = 0; ok && j < nkv; ++j) {
-        const int vs = j % C::kVStages, vph = (j / C::kVStages) & 1;
-        const int ks1 = (j + 1) % C::kKStages, kph1 = ((j + 1) / C::kKStages) & 1;
-        if (!(ok = mbar_wait(bar(C::kBarVFull + vs), vph, w, kSiteMmaV))) break;
+      // K runs one tile ahead of V: S(j+1) is issued during KV step j.
+      for (int j = 0; j <= nkv; ++j) {
+        if (j < nkv) {
+          const int ks = j % C::kKStages, kph = (j / C::kKStages) & 1;
+          if (!mbar_wait_warp(bar(C::kBarKEmpty + ks), kph ^ 1, w, kSiteLoadK)) break;
+          if (elected) {
+            mbar_arrive_expect_tx(bar(C::kBarKFull + ks), T::kTileBytes);
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int ni = i == 0 ? n0 : n1;
-          if (j < ni) {
-            if (!(ok = mbar_wait(bar(C::kBarPFull + i), j & 1, w, kSiteMmaP))) break;
-            tc_fence_after();
-            issue_pv(i, vs, j > 0);
-            if (j + 1 < ni) {
-              if (!(ok = mbar_wait(bar(C::kBarKFull + ks1), kph1, w, kSiteMmaK))) break;
-              issue_s(i, ks1);
-              mma_commit(bar(C::kBarSFull + i));
-            } else {
-              mma_commit(bar(C::kBarOFull + i));
-            }
+            for (int ch = 0; ch < T::kChunks; ++ch)
+              tma_load_3d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
+                          ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + ks));
           }
         }
-        if (!ok) break;
-        mma_commit(bar(C::kBarVEmpty + vs));
-        if (j + 1 < nkv) mma_commit(bar(C::kBarKEmpty + ks1));
+        if (j > 0) {
+          const int jv = j - 1;
+          const int vs = jv % C::kVStages, vph = (jv / C::kVStages) & 1;
+          if (!mbar_wait_warp(bar(C::kBarVEmpty + vs), vph ^ 1, w, kSiteLoadV)) break;
+          if (elected) {
+            mbar_arrive_expect_tx(bar(C::kBarVFull + vs), T::kTileBytes);
+#pragma unroll
+            for (int ch = 0; ch < T::kChunks; ++ch)
+              tma_load_3d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
+                          ch * T::kChunkElems, jv * 128, bh, bar(C::kBarVFull + vs));
+          }
+        }
+      }
+    } else if (warp == 8) {
+      // ---------------------------------------------------------------- MMA issuer
+      // (whole warp, converged; only the elected lane issues MMAs and commits)
+      const uint32_t elected = elect_one();
+      // Issue order per KV step j (the tensor pipe executes in issue order):
+      //   [group 1 copied S1(j)]   S0(j+1)     [P0(j) ready]  O0 += P0(j) V_j
+      //   [group 0 copied S0(j+1)] S1(j+1)     [P1(j) ready]  O1 += P1(j) V_j
+      // i.e. the waits follow the order in which the two softmax groups, half a step apart,
+      // produce their events.
+      int prev_i = -1, prev_j = 0;  // the S product issued last: S must be copied out first
+      bool ok = true;
+      auto issue_s = [&](int i, int j) {
+        const int ks = j % C::kKStages, kph = (j / C::kKStages) & 1;
+        if (!(ok = mbar_wait_warp(bar(C::kBarKFull + ks), kph, w, kSiteMmaK))) return;
+        if (prev_i >= 0) {
+          if (!(ok = mbar_wait_warp(bar(C::kBarSFree + prev_i), prev_j & 1, w, kSiteMmaSFree)))
+            return;
+          tc_fence_after();
+        }
+        FA2_TRACE_EVENT(traced && elected, j * 16 + 4 + i);
+        issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS,
+                                   smem_base + C::kOffQ + i * T::kTileBytes,
+                                   smem_base + C::kOffK + ks * T::kTileBytes);
+        if (elected) {
+          mma_commit(bar(C::kBarSFull + i));
+          // last product that reads K_j: tile 1's if it has a tile j, else tile 0's
+          if (i == 1 || j >= n1) mma_commit(bar(C::kBarKEmpty + ks));
+        }
+        prev_i = i;
+        prev_j = j;
+        FA2_TRACE_EVENT(traced && elected, j * 16 + 0 + 2 * i);
+      };
+      auto issue_pv = [&](int i, int j) {
+        const int vs = j % C::kVStages, vph = (j / C::kVStages) & 1;
+        if (!(ok = mbar_wait_warp(bar(C::kBarVFull + vs), vph, w, kSiteMmaV))) return;
+        if (!(ok = mbar_wait_warp(bar(C::kBarPFull + i), j & 1, w, kSiteMmaP))) return;
+        tc_fence_after();
+        FA2_TRACE_EVENT(traced && elected, j * 16 + 6 + i);
+        issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColO + i * D,
+                                   tmem_base + C::kColP + i * 64, 32,
+                                   smem_base + C::kOffV + vs * T::kTileBytes, j > 0);
+        if (elected) {
+          mma_commit(bar(C::kBarPvDone + i));
+          if (i == 1 || j >= n1) mma_commit(bar(C::kBarVEmpty + vs));
+        }
+        FA2_TRACE_EVENT(traced && elected, j * 16 + 1 + 2 * i);
+      };
+      ok = mbar_wait_warp(bar(C::kBarQFull), 0, w, kSiteMmaQ);
+      if (ok) issue_s(0, 0);
+      if (ok && has1) issue_s(1, 0);
+      for (int j = 0; ok && j < nkv; ++j) {
+        if (j + 1 < n0) issue_s(0, j + 1);
+        if (ok && j < n0) issue_pv(0, j);
+        if (ok && j + 1 < n1) issue_s(1, j + 1);
+        if (ok && j < n1) issue_pv(1, j);
       }
     }
     __syncwarp();
-  }
   } else {
     // ------------------------------------------------------------------ softmax groups
     reg_inc<208>();
@@ -210,19 +253,25 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const int nj = wg == 0 ? n0 : n1;
     const int r = (warp & 3) * 32 + lane;  // row inside the Q tile = tensor-memory lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tS = tmem_base + lane_base + C::kColS + wg * 128;
+    const uint32_t tS = tmem_base + lane_base + C::kColS;
+    const uint32_t tP = tmem_base + lane_base + C::kColP + wg * 64;
     const uint32_t tO = tmem_base + lane_base + C::kColO + wg * D;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < nj; ++j) {
       if (!(ok = mbar_wait_warp(bar(C::kBarSFull + wg), j & 1, w, kSiteSoftS))) break;
       tc_fence_after();
+      FA2_TRACE_EVENT(traced && (warp & 3) == 0 && lane == 0, j * 16 + (wg ? 13 : 8));
       uint32_t sr[128];
       tmem_ld_x32(tS + 0, sr + 0);
       tmem_ld_x32(tS + 32, sr + 32);
       tmem_ld_x32(tS + 64, sr + 64);
       tmem_ld_x32(tS + 96, sr + 96);
       tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarSFree + wg));  // S may be overwritten now
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, j * 16 + 9);
       float* s = reinterpret_cast<float*>(sr);
       if (j == qt) {  // diagonal tile: keep col <= row
 #pragma unroll
@@ -238,11 +287,16 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       }
       const float m_new = fmaxf(max3(m_run, mx[0], mx[1]), fmaxf(mx[2], mx[3]));
       const bool need = (m_new - m_run) * scale_log2 > kRescaleThreshold;
+      bool pv_waited = false;
       if (__any_sync(0xffffffffu, need)) {
         const float alpha = ex2((m_run - m_new) * scale_log2);
         l_run *= alpha;
         m_run = m_new;
         if (j > 0) {
+          // O_i must be at rest: wait for O_i += P_i(j-1) V_(j-1)
+          if (!(ok = mbar_wait_warp(bar(C::kBarPvDone + wg), (j - 1) & 1, w, kSiteSoftPv))) break;
+          tc_fence_after();
+          pv_waited = true;
 #pragma unroll
           for (int c0 = 0; c0 < D; c0 += 32) {
             uint32_t orr[32];
@@ -254,31 +308,40 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
           }
         }
       }
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, j * 16 + 10);
       // p = 2^(s*c - m*c) with packed fp32x2 FMAs; row sum in four independent packed chains.
       const float2 sc2 = make_float2(scale_log2, scale_log2);
       const float2 nm2 = make_float2(-m_run * scale_log2, -m_run * scale_log2);
       float2 acc[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+      uint32_t pk[64];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float2 t = __ffma2_rn(make_float2(s[64 * h + 2 * c], s[64 * h + 2 * c + 1]), sc2, nm2);
+      for (int c = 0; c < 64; ++c) {
+        float2 t = __ffma2_rn(make_float2(s[2 * c], s[2 * c + 1]), sc2, nm2);
+        if ((c & 7) < FA2_FWD_POLY_PAIRS_PER_8) {
+          t = ex2_poly2(t);
+        } else {
           t.x = ex2(t.x);
           t.y = ex2(t.y);
-          acc[c & 3] = __fadd2_rn(acc[c & 3], t);
-          pk[c] = pack2<BF16>(t.x, t.y);
         }
-        tmem_st_x32(tS + 32 * h, pk);
+        acc[c & 3] = __fadd2_rn(acc[c & 3], t);
+        pk[c] = pack2<BF16>(t.x, t.y);
       }
+      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, j * 16 + 11);
+      if (j > 0 && !pv_waited) {
+        // P_i still feeds O_i += P_i(j-1) V_(j-1) until that product has completed
+        if (!(ok = mbar_wait_warp(bar(C::kBarPvDone + wg), (j - 1) & 1, w, kSiteSoftPv))) break;
+      }
+      tmem_st_x32(tP, pk);
+      tmem_st_x32(tP + 32, pk + 32);
       tmem_wait_st();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarPFull + wg));
+      FA2_TRACE_EVENT(traced && (warp & 3) == 0 && lane == 0, j * 16 + (wg ? 14 : 12));
       const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
       l_run += (a01.x + a01.y) + (a23.x + a23.y);
     }
-    if (ok && nj > 0 && mbar_wait_warp(bar(C::kBarOFull + wg), 0, w, kSiteSoftO)) {
+    if (ok && nj > 0 && mbar_wait_warp(bar(C::kBarPvDone + wg), (nj - 1) & 1, w, kSiteSoftO)) {
       tc_fence_after();
       const float inv_l = 1.0f / l_run;
       // Stage the tile through the (now idle) Q buffer in the swizzled layout the output
@@ -351,6 +414,12 @@ cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtens
 }
 
 }  // namespace
+
+#ifdef FA2_TRACE
+extern "C" int fa2_trace_read_fwd(long long* out, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n));
+}
+#endif
 
 cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, const CUtensorMap& to, float* lse, int* status,

@@ -1,58 +1,84 @@
-// MMA issue sequences shared by the attention kernels.  They are deliberately not inlined:
-// each call site would otherwise keep a set of 64-bit descriptors live in the single issuing
-// thread and drive up the register count of the whole kernel.
+// MMA issue sequences shared by the attention kernels.
+//
+// Every function here is called by the WHOLE MMA warp, converged; `elected` (elect_one())
+// is non-zero in the one lane that actually issues.  The issuing warp shares its scheduler
+// with busy compute warps, so every instruction it spends per MMA delays the tensor pipe.  Each sequence therefore builds the
+// constant upper word of its shared-memory descriptors once and derives the eight per-step
+// descriptors with one 32-bit add each (the start-address field is the only part that moves,
+// and it cannot carry out of its 14 bits for addresses below 256 KiB).
 #pragma once
 #include "common.cuh"
 #include "ptx.cuh"
 
 namespace fa2 {
 
+// 64-bit shared-memory descriptor from its two words.
+__device__ __forceinline__ uint64_t desc_from_words(uint32_t lo, uint32_t hi) {
+  return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+// Upper word: stride byte offset >> 4 in bits [0,14), version 1 at bit 14, swizzle at [29,32).
+__host__ __device__ constexpr uint32_t desc_hi_word(uint32_t sbo_bytes, uint32_t swizzle) {
+  return ((sbo_bytes >> 4) & 0x3FFFu) | (1u << 14) | (swizzle << 29);
+}
+// Lower word: start address >> 4 in bits [0,14), leading byte offset >> 4 in bits [16,30).
+__device__ __forceinline__ uint32_t desc_lo_word(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+
 // acc[128, 128] = A[128 rows, D] * B[128 rows, D]^T.  Both tiles are K-major (row = M / N
 // index, the contiguous dimension is the reduction index d), as TMA stages a [128, D] tile.
 template <int D, bool BF16>
-__device__ __forceinline__ void issue_rows_x_rows(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr) {
+__device__ __forceinline__ void issue_rows_x_rows(uint32_t elected, uint32_t d_tmem,
+                                                  uint32_t a_addr, uint32_t b_addr) {
   using T = Tile<D>;
   constexpr uint32_t idesc = make_idesc(128, 128, BF16, false, false);
+  constexpr uint32_t hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
+  const uint32_t a_lo = desc_lo_word(a_addr, 16), b_lo = desc_lo_word(b_addr, 16);
 #pragma unroll
   for (int k = 0; k < D / 16; ++k) {
-    const uint32_t off =
-        (k / T::kKStepsPerChunk) * T::kChunkTileBytes + (k % T::kKStepsPerChunk) * 32;
-    mma_ss(d_tmem, make_smem_desc(a_addr + off, 16, T::kAtomBytes, T::kSwizzleMode),
-           make_smem_desc(b_addr + off, 16, T::kAtomBytes, T::kSwizzleMode), idesc, k > 0);
+    constexpr int kpc = T::kKStepsPerChunk;
+    const uint32_t off16 = ((k / kpc) * T::kChunkTileBytes + (k % kpc) * 32) >> 4;
+    if (elected)
+      mma_ss(d_tmem, desc_from_words(a_lo + off16, hi), desc_from_words(b_lo + off16, hi), idesc,
+             k > 0 ? 1u : 0u);
   }
 }
 
 // acc[128, D] (+)= A[128, 128] * B[128 rows, D].  A is 16-bit in tensor memory, two values per
-// column: reduction indices 0..63 at columns a_col .. a_col+31 and 64..127 at a_col+a_col_half ..
+// column: reduction indices 0..63 at columns a_tmem .. +31 and 64..127 at a_tmem + a_col_half ..
 // (+31).  B is a staged [128, D] tile used MN-major (row = reduction index, d contiguous).
 template <int D, bool BF16>
-__device__ __forceinline__ void issue_tmem_x_tile(uint32_t d_tmem, uint32_t a_tmem,
-                                               uint32_t a_col_half, uint32_t b_addr,
-                                               uint32_t accumulate) {
+__device__ __forceinline__ void issue_tmem_x_tile(uint32_t elected, uint32_t d_tmem,
+                                                  uint32_t a_tmem, uint32_t a_col_half,
+                                                  uint32_t b_addr, uint32_t accumulate) {
   using T = Tile<D>;
   constexpr uint32_t idesc = make_idesc(128, D, BF16, false, true);
+  constexpr uint32_t hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
+  const uint32_t b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint32_t a = a_tmem + (k < 4 ? k * 8 : a_col_half + (k - 4) * 8);
-    mma_ts(d_tmem, a,
-           make_smem_desc(b_addr + k * 2 * T::kAtomBytes, T::kChunkTileBytes, T::kAtomBytes,
-                          T::kSwizzleMode),
-           idesc, (accumulate || k > 0) ? 1u : 0u);
+    if (elected)
+      mma_ts(d_tmem, a, desc_from_words(b_lo + ((k * 2 * T::kAtomBytes) >> 4), hi), idesc,
+             k > 0 ? 1u : accumulate);
   }
 }
 
 // acc[128, D] = A^T * B with A = [128 rows (reduction), 128] 16-bit tile written by threads as
 // two swizzled [128][64] chunk tiles (MN-major A) and B a staged [128, D] tile (MN-major B).
 template <int D, bool BF16>
-__device__ __forceinline__ void issue_tileT_x_tile(uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr) {
+__device__ __forceinline__ void issue_tileT_x_tile(uint32_t elected, uint32_t d_tmem,
+                                                   uint32_t a_addr, uint32_t b_addr) {
   using T = Tile<D>;
   constexpr uint32_t idesc = make_idesc(128, D, BF16, true, true);
+  constexpr uint32_t a_hi = desc_hi_word(1024, kSwizzle128B);
+  constexpr uint32_t b_hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
+  const uint32_t a_lo = desc_lo_word(a_addr, 16384), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
 #pragma unroll
   for (int k = 0; k < 8; ++k)
-    mma_ss(d_tmem, make_smem_desc(a_addr + k * 2048, 16384, 1024, kSwizzle128B),
-           make_smem_desc(b_addr + k * 2 * T::kAtomBytes, T::kChunkTileBytes, T::kAtomBytes,
-                          T::kSwizzleMode),
-           idesc, k > 0);
+    if (elected)
+      mma_ss(d_tmem, desc_from_words(a_lo + ((k * 2048) >> 4), a_hi),
+             desc_from_words(b_lo + ((k * 2 * T::kAtomBytes) >> 4), b_hi), idesc, k > 0 ? 1u : 0u);
 }
 
 }  // namespace fa2

@@ -82,6 +82,24 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, co
 }
 
 // ----------------------------------------------------------------------------------------
+// Timeline tracing for pipeline tuning.  Compiled out unless the library is built with
+// -DFA2_TRACE; then FA2_TRACE_EVENT(cond, slot) stores clock64() of the calling thread in a
+// per-translation-unit buffer that a fa2_trace_read_* entry point copies out.
+// ----------------------------------------------------------------------------------------
+#ifdef FA2_TRACE
+constexpr int kTraceSlots = 16384;
+static __device__ long long g_trace[kTraceSlots];
+#define FA2_TRACE_EVENT(cond, slot)                                   \
+  do {                                                                \
+    if ((cond) && (slot) < fa2::kTraceSlots) fa2::g_trace[(slot)] = clock64(); \
+  } while (0)
+#else
+#define FA2_TRACE_EVENT(cond, slot) \
+  do {                              \
+  } while (0)
+#endif
+
+// ----------------------------------------------------------------------------------------
 // Proxy fences and named barriers
 // ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -146,6 +164,19 @@ __device__ __forceinline__ void tmem_wait_ld() {
 }
 __device__ __forceinline__ void tmem_wait_st() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// One lane of a converged warp gets a non-zero result.  The MMA warp runs its whole role
+// convergently and predicates only the tcgen05.mma / commit instructions on this flag: that
+// keeps descriptor arithmetic warp-uniform (cheap for the scheduler) instead of burying it in
+// a single-lane divergent branch, where the issuing warp is starved by busy compute warps.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred;
 }
 // Arrive on `bar` once every MMA issued so far by this thread has completed.
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
@@ -257,6 +288,26 @@ __device__ __forceinline__ float lg2(float x) {
   float y;
   asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+// 2^x for a pair of values on the FMA pipe instead of the MUFU: round-to-nearest split
+// x = n + f, f in [-0.5, 0.5], degree-3 minimax polynomial for 2^f (relative error 7.5e-5,
+// below half an ulp of both 16-bit formats), exponent added with integer arithmetic.  Inputs
+// are clamped at -126, so -inf gives 2^-126 (~1e-38) rather than exactly 0.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  const float2 magic = make_float2(12582912.f, 12582912.f);  // 1.5 * 2^23
+  const float2 nmagic = make_float2(-12582912.f, -12582912.f);
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 t = __fadd2_rn(x, magic);
+  const float2 n = __fadd2_rn(t, nmagic);
+  const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 p = __ffma2_rn(make_float2(0.055171407759189606f, 0.055171407759189606f), f,
+                        make_float2(0.2426110953092575f, 0.2426110953092575f));
+  p = __ffma2_rn(p, f, make_float2(0.6932610273361206f, 0.6932610273361206f));
+  p = __ffma2_rn(p, f, make_float2(0.9999280571937561f, 0.9999280571937561f));
+  p.x = __uint_as_float(__float_as_uint(p.x) + (__float_as_uint(t.x) << 23));
+  p.y = __uint_as_float(__float_as_uint(p.y) + (__float_as_uint(t.y) << 23));
+  return p;
 }
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;

@@ -19,7 +19,8 @@ def test_mma_operand_forms(form, d, dtype):
     g = torch.Generator().manual_seed(100 * form + d)
     a = torch.randn(128, d if form == 0 else 128, generator=g).to(dtype)
     b = torch.randn(128, d, generator=g).to(dtype)
-    ref = {0: a.double() @ b.double().T, 1: a.double() @ b.double(), 2: a.double().T @ b.double()}[form]
+    ad64, bd64 = a.double(), b.double()
+    ref = ad64 @ bd64.T if form == 0 else (ad64 @ bd64 if form == 1 else ad64.T @ bd64)
     ad, bd = a.cuda(), b.cuda()
     c = torch.full(ref.shape, float("nan"), device="cuda", dtype=torch.float32)
     rc = _lib.lib().fa2_selftest_mma(form, ad.data_ptr(), bd.data_ptr(), c.data_ptr(), d,
