@@ -25,8 +25,20 @@
 #include "mma_issue.cuh"
 #include "ptx.cuh"
 
+#ifndef FA2_BWD_POLY_PAIRS_PER_8
+#define FA2_BWD_POLY_PAIRS_PER_8 4  // of every 8 column pairs, this many use ex2_poly2
+#endif
+
 namespace fa2 {
 namespace {
+
+// 2^x for column pair `c` (compile-time index after unrolling): a fixed share of the pairs
+// goes to the FMA-pipe polynomial, the rest to the MUFU, because 128 x 128 exponentials per
+// tile pair would otherwise keep the MUFU (16 / clk / SM) busy for 1024 cycles.
+__device__ __forceinline__ float2 exp2_pair(float2 x, int c) {
+  if ((c & 7) < FA2_BWD_POLY_PAIRS_PER_8) return ex2_poly2(x);
+  return make_float2(ex2(x.x), ex2(x.y));
+}
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst_smem, const void* src, uint32_t bytes,
                                              uint32_t bar) {
@@ -85,7 +97,7 @@ __device__ __forceinline__ void store_rows_16bit(uint32_t tmem_row_addr, uint8_t
 template <int D, bool FUSE>
 struct DkdvCfg {
   using T = Tile<D>;
-  static constexpr int kStages = 2;  // Q (+rowstats) ring and dO ring
+  static constexpr int kStages = 2;  // Q (+rowstats) ring and dO ring (the code relies on 2)
   static constexpr int kThreads = FUSE ? 512 : 384;
   static constexpr int kMmaWarp = FUSE ? 12 : 8;
   static constexpr int kLoadWarp = kMmaWarp + 1;
@@ -171,9 +183,9 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
     mbar_init(bar(C::kBarKV), 1);
     for (int i = 0; i < C::kStages; ++i) {
       mbar_init(bar(C::kBarQFull + i), 1);
-      mbar_init(bar(C::kBarQEmpty + i), 1);
+      mbar_init(bar(C::kBarQEmpty + i), 2);   // St (warp X) and dK (warp Y) both done
       mbar_init(bar(C::kBarDOFull + i), 1);
-      mbar_init(bar(C::kBarDOEmpty + i), 1);
+      mbar_init(bar(C::kBarDOEmpty + i), 2);  // dV (warp X) and dPt (warp Y) both done
     }
     mbar_init(bar(C::kBarStFull), 1);
     mbar_init(bar(C::kBarDptFull), 1);
@@ -181,7 +193,7 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
     mbar_init(bar(C::kBarDsReady), 8);
     mbar_init(bar(C::kBarDqFull), 1);
     mbar_init(bar(C::kBarDqDrained), 4);
-    mbar_init(bar(C::kBarDone), 1);
+    mbar_init(bar(C::kBarDone), 2);  // last dV (warp X) and last dK (warp Y)
     *abort_flag = 0;
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -238,84 +250,101 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
                         ch * T::kChunkElems, qt * 128, bh, bar(C::kBarDOFull + s));
         }
       }
-    } else if (warp == C::kMmaWarp) {
-      // Whole warp, converged; only the elected lane issues MMAs and commits.
+    } else if (warp == C::kMmaWarp || warp == C::kMmaWarp + 2) {
+      // Two MMA-issuing warps, one per dependency chain (whole warp converged, the elected
+      // lane issues).  The chains touch disjoint tensor-memory columns, so no ordering
+      // between the two instruction streams is needed and neither waits behind the other:
+      //   warp X:  [Pt(i) ready]  dV += Pt dO_i,  St(i+1) = K Q_(i+1)^T         (St / Pt / dV)
+      //   warp Y:  [dSt(i) ready] dK += dSt Q_i, (dQ_i = dS K), dPt(i+1) = V dO_(i+1)^T
+      //            (dPt / dSt / dK; in the fused kernel dQ shares the dPt columns, so dPt(i+1)
+      //            waits until the reduction group has drained dQ_i)
+      // Within a chain the in-order tensor pipe protects the write-after-read hazards
+      // (St(i+1) over Pt(i), dPt(i+1) / dQ_i over dSt(i)).
       const uint32_t elected = elect_one();
       const uint32_t ka = smem_base + C::kOffK, va = smem_base + C::kOffV;
       auto commit = [&](int b) {
         if (elected) mma_commit(bar(b));
       };
-      // St / dPt: [128 kv, 128 q] = (K or V tile) x (Q or dO tile)^T, both K-major.
-      auto issue_t = [&](uint32_t col, uint32_t a_base, uint32_t b_base) {
-        issue_rows_x_rows<D, BF16>(elected, tmem_base + col, a_base, b_base);
-      };
-      // dV / dK: [128 kv, D] += (16-bit Pt or dSt in tensor memory) x (dO or Q tile, MN-major).
-      auto issue_acc = [&](uint32_t col_d, uint32_t col_a, uint32_t b_base, bool accumulate) {
-        issue_tmem_x_tile<D, BF16>(elected, tmem_base + col_d, tmem_base + col_a, 64, b_base,
-                                   accumulate);
-      };
-      bool ok = mbar_wait_warp(bar(C::kBarKV), 0, w, kBSiteMmaKV) &&
-                mbar_wait_warp(bar(C::kBarQFull + 0), 0, w, kBSiteMmaQ);
-      if (ok) {
-        issue_t(C::kColSt, ka, smem_base + C::kOffQ);
-        commit(C::kBarStFull);
-        ok = mbar_wait_warp(bar(C::kBarDOFull + 0), 0, w, kBSiteMmaDO);
-      }
-      if (ok) {
-        issue_t(C::kColDpt, va, smem_base + C::kOffDO);
-        commit(C::kBarDptFull);
-      }
-      // Issue order inside one iteration (the tensor pipe executes in issue order, so the
-      // order decides what can overlap):
-      //   plain:  [Pt ready] dV(i), St(i+1)                 [dSt ready] dK(i), dPt(i+1)
-      //   fused:  [Pt ready] dV(i), [dQ(i-1) drained] dPt(i), St(i+1)   [dSt ready] dK(i), dQ(i)
-      // In the fused kernel dPt shares its columns with dQ, so dPt(i) has to wait for the
-      // reduction group; issuing dV(i) first keeps the pipe busy during that drain.
-      for (int ii = 0; ok && ii < nq; ++ii) {
-        const int s = ii % C::kStages, ph = (ii / C::kStages) & 1;
-        const int s1 = (ii + 1) % C::kStages, ph1 = ((ii + 1) / C::kStages) & 1;
-        const uint32_t qa = smem_base + C::kOffQ + s * T::kTileBytes;
-        const uint32_t doa = smem_base + C::kOffDO + s * T::kTileBytes;
-        if (!(ok = mbar_wait_warp(bar(C::kBarPtReady), ii & 1, w, kBSiteMmaPt))) break;
-        tc_fence_after();
-        FA2_TRACE_EVENT(traced && elected, ii * 16 + 0);
-        issue_acc(C::kColDV, C::kColSt, doa, ii > 0);  // dV += Pt dO_i
-        if constexpr (FUSE) {
-          if (ii > 0) {
-            if (!(ok = mbar_wait_warp(bar(C::kBarDqDrained), (ii - 1) & 1, w, kBSiteMmaDrain))) break;
-            tc_fence_after();
-            FA2_TRACE_EVENT(traced && elected, ii * 16 + 4);
-            if (!(ok = mbar_wait_warp(bar(C::kBarDOFull + s), ph, w, kBSiteMmaDO))) break;
-            issue_t(C::kColDpt, va, doa);  // dPt(i)
+      bool ok = mbar_wait(bar(C::kBarKV), 0, w, kBSiteMmaKV);
+      int s = 0, ph = 0;  // ring stage / phase of Q tile ii (both rings advance together)
+      if (warp == C::kMmaWarp) {
+        // ------------------------------------------------------------ warp X
+        if (ok && (ok = mbar_wait(bar(C::kBarQFull + 0), 0, w, kBSiteMmaQ))) {
+          issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColSt, ka, smem_base + C::kOffQ);
+          commit(C::kBarStFull);
+          commit(C::kBarQEmpty + 0);
+        }
+        for (int ii = 0; ok && ii < nq; ++ii) {
+          const int s1 = s ^ 1, ph1 = ph ^ s;  // stage / phase of tile ii+1 (two stages)
+          const uint32_t doa = smem_base + C::kOffDO + s * T::kTileBytes;
+          if (!(ok = mbar_wait(bar(C::kBarDOFull + s), ph, w, kBSiteMmaDO))) break;
+          if (!(ok = mbar_wait(bar(C::kBarPtReady), ii & 1, w, kBSiteMmaPt))) break;
+          tc_fence_after();
+          FA2_TRACE_EVENT(traced && elected, ii * 16 + 0);
+          issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDV, tmem_base + C::kColSt, 64, doa,
+                                     ii > 0);  // dV += Pt dO_i
+          commit(C::kBarDOEmpty + s);
+          if (ii + 1 < nq) {
+            if (!(ok = mbar_wait(bar(C::kBarQFull + s1), ph1, w, kBSiteMmaQ))) break;
+            issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColSt, ka,
+                                       smem_base + C::kOffQ + s1 * T::kTileBytes);  // St(i+1)
+            commit(C::kBarStFull);
+            commit(C::kBarQEmpty + s1);
+          }
+          FA2_TRACE_EVENT(traced && elected, ii * 16 + 1);
+          ph ^= s;
+          s ^= 1;
+        }
+        if (ok) commit(C::kBarDone);
+      } else {
+        // ------------------------------------------------------------ warp Y
+        if (ok && (ok = mbar_wait(bar(C::kBarDOFull + 0), 0, w, kBSiteMmaDO))) {
+          issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColDpt, va, smem_base + C::kOffDO);
+          commit(C::kBarDptFull);
+          commit(C::kBarDOEmpty + 0);
+        }
+        for (int ii = 0; ok && ii < nq; ++ii) {
+          const int s1 = s ^ 1, ph1 = ph ^ s;
+          const uint32_t qa = smem_base + C::kOffQ + s * T::kTileBytes;
+          if (!(ok = mbar_wait(bar(C::kBarQFull + s), ph, w, kBSiteMmaQ))) break;
+          if (!(ok = mbar_wait(bar(C::kBarDsReady), ii & 1, w, kBSiteMmaDs))) break;
+          if constexpr (!FUSE) {
+            // St(i+1) sits on the critical chain St -> Pt -> dV -> St; let warp X get it into
+            // the in-order pipe first, dK and dPt(i+1) then run under the next exponentials.
+            if (ii + 1 < nq) {
+              if (!(ok = mbar_wait(bar(C::kBarStFull), (ii + 1) & 1, w, kBSiteMmaQ))) break;
+            }
+          }
+          tc_fence_after();
+          FA2_TRACE_EVENT(traced && elected, ii * 16 + 2);
+          issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDK, tmem_base + C::kColDpt, 64, qa,
+                                     ii > 0);  // dK += dSt Q_i
+          commit(C::kBarQEmpty + s);
+          if constexpr (FUSE) {
+            // dQ_i[128 q, D] = dS[q, kv] * K[kv, d]: A = dS^T tile in smem (q contiguous ->
+            // MN-major), B = K tile (d contiguous -> MN-major); lands over the dPt columns.
+            issue_tileT_x_tile<D, BF16>(elected, tmem_base + C::kColDpt, smem_base + C::kOffDS, ka);
+            commit(C::kBarDqFull);
+          }
+          FA2_TRACE_EVENT(traced && elected, ii * 16 + 3);
+          if (ii + 1 < nq) {
+            if constexpr (FUSE) {
+              if (!(ok = mbar_wait(bar(C::kBarDqDrained), ii & 1, w, kBSiteMmaDrain))) break;
+              tc_fence_after();
+              FA2_TRACE_EVENT(traced && elected, ii * 16 + 4);
+            }
+            if (!(ok = mbar_wait(bar(C::kBarDOFull + s1), ph1, w, kBSiteMmaDO))) break;
+            issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColDpt, va,
+                                       smem_base + C::kOffDO + s1 * T::kTileBytes);  // dPt(i+1)
             commit(C::kBarDptFull);
+            commit(C::kBarDOEmpty + s1);
             FA2_TRACE_EVENT(traced && elected, ii * 16 + 5);
           }
+          ph ^= s;
+          s ^= 1;
         }
-        commit(C::kBarDOEmpty + s);
-        if (ii + 1 < nq) {
-          if (!(ok = mbar_wait_warp(bar(C::kBarQFull + s1), ph1, w, kBSiteMmaQ))) break;
-          issue_t(C::kColSt, ka, smem_base + C::kOffQ + s1 * T::kTileBytes);  // St(i+1)
-          commit(C::kBarStFull);
-        }
-        FA2_TRACE_EVENT(traced && elected, ii * 16 + 1);
-        if (!(ok = mbar_wait_warp(bar(C::kBarDsReady), ii & 1, w, kBSiteMmaDs))) break;
-        tc_fence_after();
-        FA2_TRACE_EVENT(traced && elected, ii * 16 + 2);
-        issue_acc(C::kColDK, C::kColDpt, qa, ii > 0);  // dK += dSt Q_i
-        commit(C::kBarQEmpty + s);
-        if constexpr (FUSE) {
-          // dQ_i[128 q, D] = dS[q, kv] * K[kv, d]: A = dS^T tile in smem (q contiguous ->
-          // MN-major), B = K tile (d contiguous -> MN-major); 16 kv rows per MMA.
-          issue_tileT_x_tile<D, BF16>(elected, tmem_base + C::kColDpt, smem_base + C::kOffDS, ka);
-          commit(C::kBarDqFull);
-        } else if (ii + 1 < nq) {
-          if (!(ok = mbar_wait_warp(bar(C::kBarDOFull + s1), ph1, w, kBSiteMmaDO))) break;
-          issue_t(C::kColDpt, va, smem_base + C::kOffDO + s1 * T::kTileBytes);  // dPt(i+1)
-          commit(C::kBarDptFull);
-        }
-        FA2_TRACE_EVENT(traced && elected, ii * 16 + 3);
+        if (ok) commit(C::kBarDone);
       }
-      if (ok) commit(C::kBarDone);
     }
     __syncwarp();
   } else if (FUSE && warp >= 8) {
@@ -381,8 +410,8 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
                                  sc2, make_float2(l.x, l.y));
           float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4 + 2]), __uint_as_float(sr[4 * c4 + 3])),
                                  sc2, make_float2(l.z, l.w));
-          p[2 * c4] = make_float2(ex2(t0.x), ex2(t0.y));
-          p[2 * c4 + 1] = make_float2(ex2(t1.x), ex2(t1.y));
+          p[2 * c4] = exp2_pair(t0, 2 * c4);
+          p[2 * c4 + 1] = exp2_pair(t1, 2 * c4 + 1);
         }
       }
       if (ii == 0) {  // diagonal tile: keep q >= kv
@@ -494,7 +523,8 @@ struct DqCfg {
   static constexpr int kBarDpFull = kBarSFull + 2;
   static constexpr int kBarDpConsumed = kBarDpFull + 1;  // 8 arrivals (one per compute warp)
   static constexpr int kBarDsReady = kBarDpConsumed + 1;  // 8 arrivals
-  static constexpr int kBarDone = kBarDsReady + 1;
+  static constexpr int kBarDqDone = kBarDsReady + 1;      // dQ += dS(j) K_j completed
+  static constexpr int kBarDone = kBarDqDone + 1;
   static constexpr int kNumBars = kBarDone + 1;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
   static constexpr int kColS = 0;     // score buffers at 0 and 128; dS (16-bit) overwrites them
@@ -535,7 +565,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
     mbar_init(bar(C::kBarQ), 1);
     for (int i = 0; i < C::kKStages; ++i) {
       mbar_init(bar(C::kBarKFull + i), 1);
-      mbar_init(bar(C::kBarKEmpty + i), 1);
+      mbar_init(bar(C::kBarKEmpty + i), 2);  // S(j) (warp X) and dQ(j) (warp Y) both done
     }
     for (int i = 0; i < C::kVStages; ++i) {
       mbar_init(bar(C::kBarVFull + i), 1);
@@ -546,6 +576,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
     mbar_init(bar(C::kBarDpFull), 1);
     mbar_init(bar(C::kBarDpConsumed), 8);
     mbar_init(bar(C::kBarDsReady), 8);
+    mbar_init(bar(C::kBarDqDone), 1);
     mbar_init(bar(C::kBarDone), 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -602,61 +633,83 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
         }
       }
     } else if (warp == C::kMmaWarp) {
-      // Whole warp, converged; only the elected lane issues MMAs and commits.
+      // ------------------------------------------------------------ warp X: S and dP products
+      // (whole warp converged, the elected lane issues).  dQ products are issued by warp
+      // kMmaWarp + 2 so that neither stream waits behind the other's barriers; the one
+      // hazard between the streams, S(j+2) overwriting dS(j) while dQ(j) still reads it, is
+      // covered by the dq_done barrier.
       const uint32_t elected = elect_one();
       auto commit = [&](int b) {
         if (elected) mma_commit(bar(b));
       };
       const uint32_t qa = smem_base + C::kOffQ, doa = smem_base + C::kOffDO;
-      auto k_addr = [&](int j) { return smem_base + C::kOffK + (j % C::kKStages) * T::kTileBytes; };
-      auto k_wait = [&](int j) {
-        return mbar_wait_warp(bar(C::kBarKFull + j % C::kKStages), (j / C::kKStages) & 1, w, kBSiteMmaKV);
-      };
-      auto issue_s = [&](int j) {  // S(j) -> score buffer j%2
-        issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS + (j & 1) * 128, qa, k_addr(j));
+      int ks = 0, kph = 0, vs = 0, vph = 0;  // ring positions of the next K / V tile to use
+      auto issue_s = [&](int j) -> bool {   // S(j) -> score buffer j%2, K ring position (ks, kph)
+        if (!mbar_wait(bar(C::kBarKFull + ks), kph, w, kBSiteMmaKV)) return false;
+        issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS + (j & 1) * 128, qa,
+                                   smem_base + C::kOffK + ks * T::kTileBytes);
         commit(C::kBarSFull + (j & 1));
+        commit(C::kBarKEmpty + ks);
+        if (++ks == C::kKStages) {
+          ks = 0;
+          kph ^= 1;
+        }
+        return true;
       };
-      auto issue_dp = [&](int j) {  // dP(j); V_j is free afterwards
-        const int vs = j % C::kVStages;
+      auto issue_dp = [&]() -> bool {  // dP of the next V tile; V is free afterwards
+        if (!mbar_wait(bar(C::kBarVFull + vs), vph, w, kBSiteMmaDO)) return false;
         issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColDp, doa,
                                    smem_base + C::kOffV + vs * T::kTileBytes);
         commit(C::kBarDpFull);
         commit(C::kBarVEmpty + vs);
+        if (++vs == C::kVStages) {
+          vs = 0;
+          vph ^= 1;
+        }
+        return true;
       };
-      auto v_wait = [&](int j) {
-        return mbar_wait_warp(bar(C::kBarVFull + j % C::kVStages), (j / C::kVStages) & 1, w, kBSiteMmaDO);
-      };
-      bool ok = mbar_wait_warp(bar(C::kBarQ), 0, w, kBSiteMmaQ) && k_wait(0);
-      if (ok) {
-        issue_s(0);
-        ok = v_wait(0);
-      }
-      if (ok) {
-        issue_dp(0);
-        if (nkv > 1 && (ok = k_wait(1))) issue_s(1);
-      }
+      bool ok = mbar_wait(bar(C::kBarQ), 0, w, kBSiteMmaQ);
+      ok = ok && issue_s(0) && issue_dp();
+      if (ok && nkv > 1) ok = issue_s(1);
       for (int j = 0; ok && j < nkv; ++j) {
         if (j + 1 < nkv) {
           // dP columns are free once every compute warp has read dP(j)
-          if (!(ok = mbar_wait_warp(bar(C::kBarDpConsumed), j & 1, w, kBSiteMmaDrain))) break;
+          if (!(ok = mbar_wait(bar(C::kBarDpConsumed), j & 1, w, kBSiteMmaDrain))) break;
           tc_fence_after();
           FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 0);
-          if (!(ok = v_wait(j + 1))) break;
-          issue_dp(j + 1);
+          if (!(ok = issue_dp())) break;
           FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 1);
         }
-        if (!(ok = mbar_wait_warp(bar(C::kBarDsReady), j & 1, w, kBSiteMmaDs))) break;
+        if (j + 2 < nkv) {
+          // score buffer j%2 holds dS(j) until dQ += dS(j) K_j has completed
+          if (!(ok = mbar_wait(bar(C::kBarDqDone), j & 1, w, kBSiteMmaDs))) break;
+          tc_fence_after();
+          if (!(ok = issue_s(j + 2))) break;
+          FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 4);
+        }
+      }
+    } else if (warp == C::kMmaWarp + 2) {
+      // ------------------------------------------------------------ warp Y: dQ += dS(j) K_j
+      const uint32_t elected = elect_one();
+      auto commit = [&](int b) {
+        if (elected) mma_commit(bar(b));
+      };
+      bool ok = true;
+      int ks = 0, kph = 0;
+      for (int j = 0; ok && j < nkv; ++j) {
+        if (!(ok = mbar_wait(bar(C::kBarKFull + ks), kph, w, kBSiteMmaKV))) break;
+        if (!(ok = mbar_wait(bar(C::kBarDsReady), j & 1, w, kBSiteMmaDs))) break;
         tc_fence_after();
         FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 2);
-        // dQ += dS(j) K_j : A = 16-bit dS over score buffer j%2, B = K_j as MN-major tile
-        issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDQ, tmem_base + C::kColS + (j & 1) * 128, 64,
-                                   k_addr(j), j > 0);
-        commit(C::kBarKEmpty + j % C::kKStages);
+        // A = 16-bit dS over score buffer j%2, B = K_j as MN-major tile
+        issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDQ, tmem_base + C::kColS + (j & 1) * 128,
+                                   64, smem_base + C::kOffK + ks * T::kTileBytes, j > 0);
+        commit(C::kBarDqDone);
+        commit(C::kBarKEmpty + ks);
         FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 3);
-        if (j + 2 < nkv) {
-          if (!(ok = k_wait(j + 2))) break;
-          issue_s(j + 2);  // reuses buffer j%2; ordered after dQ(j) by the in-order MMA pipe
-          FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 4);
+        if (++ks == C::kKStages) {
+          ks = 0;
+          kph ^= 1;
         }
       }
       if (ok) commit(C::kBarDone);
@@ -693,7 +746,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
         for (int c = 0; c < 32; ++c) {
           const float2 t = __ffma2_rn(
               make_float2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), sc2, nlse2);
-          p[c] = make_float2(ex2(t.x), ex2(t.y));
+          p[c] = exp2_pair(t, c);
         }
       }
       if (j == qt) {  // diagonal tile: keep kv <= q

