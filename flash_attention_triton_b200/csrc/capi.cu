@@ -116,6 +116,7 @@ const char* fa2_strerror(int code) {
     case FA2_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
     case FA2_ERR_SCALE: return "softmax scale must be finite and > 0";
     case FA2_ERR_WORKSPACE: return "dq_accum workspace is required when deterministic == 0";
+    case FA2_ERR_TOO_LARGE: return "problem exceeds the built-in scratch (B*H*ceil(N/128) > 4096)";
     default: break;
   }
   if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
@@ -231,3 +232,56 @@ int fa2_selftest_mma(int form, const void* a, const void* b, float* c, int D, in
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Backward without any caller-provided or allocated workspace.
+// ---------------------------------------------------------------------------------------
+namespace fa2 {
+// Row statistics (-lse*log2e, -delta) of up to kStaticRowstatTiles Q tiles live here instead
+// of in a caller buffer.  In HOST code this name is only a handle for the runtime: the real
+// device address comes from cudaGetSymbolAddress, once per device, below.
+constexpr int kStaticRowstatTiles = 4096;  // 4096 tiles x 256 floats = 4 MiB per GPU
+static __device__ __align__(256) float g_static_rowstats[kStaticRowstatTiles * 256];
+
+namespace {
+struct StaticScratch {
+  std::once_flag once;
+  float* ptr = nullptr;
+  cudaError_t err = cudaSuccess;
+};
+StaticScratch g_static_scratch[kMaxDevices];
+
+// Device address of g_static_rowstats on the CURRENT device (looked up on first use).
+int static_rowstats(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= kMaxDevices) return FA2_ERR_ARCH;
+  StaticScratch& sc = g_static_scratch[dev];
+  std::call_once(sc.once, [&] {
+    sc.err = cudaGetSymbolAddress(reinterpret_cast<void**>(&sc.ptr), g_static_rowstats);
+  });
+  if (sc.err != cudaSuccess) return static_cast<int>(sc.err);
+  if (sc.ptr == nullptr) return FA2_ERR_DRIVER;
+  *out = sc.ptr;
+  return FA2_OK;
+}
+}  // namespace
+}  // namespace fa2
+
+extern "C" int fa2_bwd_static_scratch(const void* q, const void* k, const void* v, const void* o,
+                                      const void* dout, const float* lse, void* dq, void* dk,
+                                      void* dv, int B, int H, int N, int D, int dtype, float scale,
+                                      fa2_stream_t stream) {
+  if (!q || !k || !v || !o || !dout || !lse || !dq || !dk || !dv) return FA2_ERR_NULL_POINTER;
+  if (int e = check_shape(B, H, N, D, dtype)) return e;
+  const long long tiles = static_cast<long long>(B) * H * ((N + 127) / 128);
+  if (tiles > kStaticRowstatTiles) return FA2_ERR_TOO_LARGE;
+  float* rowstats = nullptr;
+  if (int e = static_rowstats(&rowstats)) return e;
+  // Every element of the part of the array that the kernels read is rewritten by the
+  // preprocess launch (padding rows included), so nothing has to be cleared first.
+  if (int e = fa2_bwd_preprocess(o, dout, lse, rowstats, B, H, N, D, dtype, stream)) return e;
+  return fa2_bwd(q, k, v, dout, rowstats, dq, dk, dv, nullptr, B, H, N, D, dtype, scale,
+                 /*deterministic=*/1, stream);
+}

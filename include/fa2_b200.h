@@ -46,6 +46,7 @@ extern "C" {
 #define FA2_ERR_DRIVER (-8)            /* cuTensorMapEncodeTiled unavailable or failed */
 #define FA2_ERR_SCALE (-9)             /* softmax scale not finite or not > 0 */
 #define FA2_ERR_WORKSPACE (-10)        /* dq_accum is NULL although deterministic == 0 */
+#define FA2_ERR_TOO_LARGE (-11)        /* fa2_bwd_static_scratch: B*H*ceil(N/128) > 4096 */
 
 /* Opaque stream handle: pass a cudaStream_t (NULL = legacy default stream). */
 typedef void* fa2_stream_t;
@@ -122,6 +123,29 @@ int fa2_device_status(int* status_out);
  */
 int fa2_selftest_mma(int form, const void* a, const void* b, float* c,
                      int D, int dtype, fa2_stream_t stream);
+
+/*
+ * Whole deterministic backward (preprocess + dK/dV + dQ) for callers that must not allocate
+ * device memory and have no workspace to hand in: code running inside a CUDA-graph replay
+ * loop, a plugin called from a framework that owns the allocator, a real-time serving loop
+ * in which cudaMalloc (a device-wide synchronising call) is off limits.  The row statistics
+ * that fa2_bwd_preprocess normally writes into a caller buffer go into a 4 MiB array that
+ * is part of the library image on every GPU that loads it.  The caller passes only inputs
+ * (q, k, v, o, dout, lse from fa2_fwd) and outputs (dq, dk, dv); results are bit-identical
+ * to fa2_bwd_preprocess + fa2_bwd(deterministic = 1).
+ *   Limit: B*H*ceil(N/128) <= 4096 Q tiles (e.g. B*H = 64 at N = 8192); larger problems
+ *   return FA2_ERR_TOO_LARGE and launch nothing.
+ *   The first call on each device looks up the array's device address (one runtime query,
+ *   no allocation); make that first call outside any stream capture.
+ *   All calls on a device share the one array: two calls whose kernels may overlap on the
+ *   GPU (different streams, no dependency) race on it.  Calls on one stream are safe; the
+ *   array keeps the last call's contents and each call rewrites every value it reads.
+ * This entry point has no counterpart in the reference.
+ */
+int fa2_bwd_static_scratch(const void* q, const void* k, const void* v, const void* o,
+                           const void* dout, const float* lse, void* dq, void* dk, void* dv,
+                           int B, int H, int N, int D, int dtype, float scale,
+                           fa2_stream_t stream);
 
 #ifdef __cplusplus
 }
