@@ -1,0 +1,103 @@
+"""Time the UNMODIFIED reference (flash-attention-triton, installed under baseline/_ref) on this GPU.
+
+Informational arm next to bench.py: the reference's own Triton kernels through its own public
+API, same seeded inputs and FLOP convention as bench.py.  The shipped default configuration
+(256 x 256 forward tiles) may not fit Blackwell tensor memory; in that case the exception text
+is recorded and the reference is driven through its documented `flash_attention_v2_custom`
+entry point with forward tiles that fit (the backward keeps the reference's autotune list).
+
+    python baseline/reference_triton_bench.py [--workload c3] [--steps 5]
+
+Prints one JSON line per (workload, mode).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+sys.path.insert(0, str(ROOT))
+
+from bench import WORKLOADS, fwd_flops, make_inputs  # noqa: E402
+
+
+def time_ms(fn, steps):
+    for _ in range(2):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
+    ap.add_argument("--steps", type=int, default=5)
+    args = ap.parse_args()
+    try:
+        import triton
+        from flash_attention_triton import (KernelsConfigV2, flash_attention_v2,
+                                            flash_attention_v2_custom, init_to_zero_v2)
+    except Exception as exc:  # the reference or triton is not importable here
+        print(json.dumps({"impl": "reference-triton", "unavailable": repr(exc)[:300]}))
+        return
+
+    b, h, n, d, dtype, qk_mul, scale = WORKLOADS[args.workload]
+    dev = torch.device("cuda:0")
+    q, k, v, do = (t.to(dev) for t in make_inputs((b, h, n, d), dtype, 0, qk_mul))
+    f = fwd_flops(b, h, n, d)
+    cc = torch.cuda.get_device_capability()
+
+    def bwd_cfgs(seqpar):
+        return [triton.Config({"BLOCK_Q_ROWS_SIZE": bs, "BLOCK_KV_COLS_SIZE": bs, "SEQUENCE_PARALLEL": seqpar},
+                              num_warps=8, num_stages=1, pre_hook=init_to_zero_v2("DQ"))
+                for bs in (64, 128)]
+
+    for det in (True, False):
+        rec = {"impl": "reference-triton", "workload": args.workload, "deterministic": det,
+               "triton": triton.__version__, "gpu": torch.cuda.get_device_name(0)}
+        runners = [("default", lambda qq, kk, vv: flash_attention_v2(qq, kk, vv, scale, det))]
+        for bm, bn in ((128, 128), (128, 64), (64, 64)):
+            cfg = KernelsConfigV2(bm, bn, 32, 256, 32, 8, 16, 1, bwd_cfgs(not det))
+            runners.append((f"custom fwd {bm}x{bn}",
+                            lambda qq, kk, vv, cfg=cfg: flash_attention_v2_custom(qq, kk, vv, scale, {cc: cfg})))
+        best = None
+        for name, run in runners:
+            try:
+                qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+                out = run(qq, kk, vv)
+                out.backward(do)
+                torch.cuda.synchronize()
+
+                def step():
+                    o2 = run(qq, kk, vv)
+                    o2.backward(do)
+
+                ms = time_ms(step, args.steps)
+                ms_fwd = time_ms(lambda: run(qq, kk, vv), args.steps)
+                rec.setdefault("tried", {})[name] = {"fwd_bwd_ms": ms, "fwd_ms": ms_fwd}
+                if best is None or ms < best[1]:
+                    best = (name, ms, ms_fwd)
+            except Exception as exc:
+                rec.setdefault("tried", {})[name] = {"error": f"{type(exc).__name__}: {str(exc)[:160]}"}
+        if best:
+            rec.update({"config": best[0], "fwd_bwd_ms": best[1], "fwd_ms": best[2],
+                        "fwd_bwd_tflops": 3.5 * f / best[1] / 1e9, "fwd_tflops": f / best[2] / 1e9,
+                        "note": "API-level time: includes the reference's casts to fp16, memset and dq copy"})
+        print(json.dumps(rec), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -56,6 +56,18 @@ WORKLOADS = {
 METRIC = "causal attn fwd+bwd TFLOP/s, bf16 N=8192 d=128"
 
 
+# DRAM bytes (read + write) of the backward-main kernels measured by ncu on the reduced C3
+# workload (24 batch*head problems, N=8192, d=128): fused kernel 303.7 + 159.2 MB; the
+# deterministic pair 203.2 + 76.1 MB (dK/dV) plus 202.9 + 37.9 MB (dQ).
+NCU_BWD_DRAM_MB_PER_24 = {False: 303.7 + 159.2, True: 203.2 + 76.1 + 202.9 + 37.9}
+
+
+def traffic_bytes(d, det, batch_heads, n=8192):
+    if d != 128 or n != 8192:
+        return None
+    return NCU_BWD_DRAM_MB_PER_24[bool(det)] * 1e6 * batch_heads / 24.0
+
+
 def fwd_flops(b, h, n, d):
     return 4.0 * b * h * n * n * d / 2.0
 
@@ -335,7 +347,11 @@ def main():
                   else "bwd_dkdv_kernel + bwd_dq_kernel",
         "bound": "tensor", "achieved": bwd_tf, "peak": peaks["bf16"], "unit": "TFLOP/s",
         "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} burst bf16 GEMM",
-        "traffic": None,
+        "traffic": traffic_bytes(d, det, lb * lh, n),
+        "traffic_note": "dram__bytes_read+write per launch(es) of the backward-main kernel(s) from the "
+                        "ncu capture in profiles/attention_kernels_c3small_ncu.md (24 batch*head "
+                        "problems, d=128, N=8192), scaled by batch*head; null for other shapes",
+        "algorithmic_flops": 2.5 * my_fwd_flops,
         "fwd": {"achieved": fwd_tf, "frac": fwd_tf / peaks["bf16"], "ms": ms_fwd},
         "bwd_ms": ms_bwd,
         "preprocess": {"bound": "hbm", "achieved": pre_bytes / (ms_pre * 1e-3) / 1e9,
