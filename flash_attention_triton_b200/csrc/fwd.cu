@@ -96,6 +96,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   // still the tensor-memory lane quarter the hardware warp may access.
   const int warp = ((threadIdx.x >> 5) + 8) % 12;
   const int lane = threadIdx.x & 31;
+  FA2_CTA_TRACE(threadIdx.x == 0, 1);  // CTA entry
   const uint32_t smem_base = smem_u32(smem);
   if (smem_base & 1023u) {  // swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) atomicCAS(status, 0, 0x20000 | kSiteAlign);
@@ -146,6 +147,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const WaitCtx w{abort_flag, status};
+  FA2_CTA_TRACE(threadIdx.x == 0, 2);  // set-up done
 
   if (warp >= 8) {
     reg_dec<72>();  // whole warpgroup (warps 8-11) gives registers to the softmax groups
@@ -270,6 +272,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     for (int j = 0; j < nj; ++j) {
       if (!(ok = mbar_wait_warp(bar(C::kBarSFull + wg), j & 1, w, kSiteSoftS))) break;
       tc_fence_after();
+      FA2_CTA_TRACE(j == 0 && warp == 0 && lane == 0, 3);  // first scores arrived
       FA2_TRACE_EVENT(traced && (warp & 3) == 0 && lane == 0, j * 16 + (wg ? 13 : 8));
       uint32_t sr[128];
       tmem_ld_x32(tS + 0, sr + 0);
@@ -351,8 +354,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
       l_run += (a01.x + a01.y) + (a23.x + a23.y);
     }
+    FA2_CTA_TRACE(warp == 0 && lane == 0, 4);  // main loop of group 0 done
     if (ok && nj > 0 && mbar_wait_warp(bar(C::kBarPvDone + wg), (nj - 1) & 1, w, kSiteSoftO)) {
       tc_fence_after();
+      FA2_CTA_TRACE(warp == 0 && lane == 0, 5);  // last O product done
       const float inv_l = 1.0f / l_run;
       // Stage the tile through the (now idle) Q buffer in the swizzled layout the output
       // tensor map expects; each warp stores its own 32 rows.
@@ -398,8 +403,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   }
 
   // ---------------------------------------------------------------------- teardown
+  FA2_CTA_TRACE(warp == 0 && lane == 0, 6);  // group 0 epilogue done
   tc_fence_before();
   __syncthreads();
+  FA2_CTA_TRACE(threadIdx.x == 0, 7);  // all roles done
   if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
@@ -428,6 +435,9 @@ cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtens
 #ifdef FA2_TRACE
 extern "C" int fa2_trace_read_fwd(long long* out, int n) {
   return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n));
+}
+extern "C" int fa2_cta_trace_read_fwd(long long* out, int n) {
+  return static_cast<int>(cudaMemcpyFromSymbol(out, g_cta_trace, sizeof(long long) * n));
 }
 #endif
 

@@ -93,7 +93,26 @@ static __device__ long long g_trace[kTraceSlots];
   do {                                                                \
     if ((cond) && (slot) < fa2::kTraceSlots) fa2::g_trace[(slot)] = clock64(); \
   } while (0)
+// Per-CTA record (8 values per CTA): [0] SM id, [1..7] clock64 at points the kernel chooses.
+constexpr int kCtaTraceCtas = 8192;
+static __device__ long long g_cta_trace[kCtaTraceCtas * 8];
+__device__ __forceinline__ unsigned fa2_smid() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
+#define FA2_CTA_TRACE(cond, idx)                                                              \
+  do {                                                                                        \
+    const unsigned cta_ = blockIdx.y * gridDim.x + blockIdx.x;                                \
+    if ((cond) && cta_ < fa2::kCtaTraceCtas) {                                                \
+      fa2::g_cta_trace[cta_ * 8 + (idx)] = clock64();                                         \
+      if ((idx) == 1) fa2::g_cta_trace[cta_ * 8] = fa2::fa2_smid();                           \
+    }                                                                                         \
+  } while (0)
 #else
+#define FA2_CTA_TRACE(cond, idx) \
+  do {                           \
+  } while (0)
 #define FA2_TRACE_EVENT(cond, slot) \
   do {                              \
   } while (0)
