@@ -1,6 +1,7 @@
 // C ABI of the library (declared in include/fa2_b200.h): argument validation, tensor-map
 // construction and kernel dispatch.  Nothing here allocates device memory or synchronises,
 // except fa2_device_status which reads the status word back.
+#include <atomic>
 #include <cmath>
 #include <cstdint>
 #include <mutex>
@@ -12,6 +13,11 @@ namespace fa2 {
 
 // One status word per device: kernels write here when a bounded wait expires.
 __device__ int g_status_word;
+// Work counters of the tile-fetching kernels.  Every launch takes the next slot of this ring
+// and zeroes it on its stream, so launches that overlap on the device do not share a counter
+// (unless more than kWorkCounterSlots of them are in flight at once).
+constexpr int kWorkCounterSlots = 1024;
+__device__ unsigned int g_work_counters[kWorkCounterSlots];
 
 namespace {
 
@@ -40,7 +46,10 @@ EncodeTiledFn get_encode() {
 struct DeviceState {
   std::once_flag once;
   int cc_major = 0;
+  int num_sms = 0;
   int* status = nullptr;
+  unsigned int* counters = nullptr;
+  std::atomic<unsigned> next_counter{0};
   cudaError_t err = cudaSuccess;
 };
 DeviceState g_dev[kMaxDevices];
@@ -55,7 +64,11 @@ int device_state(DeviceState** out) {
   std::call_once(d.once, [&] {
     d.err = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);
     if (d.err == cudaSuccess)
+      d.err = cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (d.err == cudaSuccess)
       d.err = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.status), g_status_word);
+    if (d.err == cudaSuccess)
+      d.err = cudaGetSymbolAddress(reinterpret_cast<void**>(&d.counters), g_work_counters);
   });
   if (d.err != cudaSuccess) return static_cast<int>(d.err);
   if (d.cc_major != 10) return FA2_ERR_ARCH;
@@ -81,6 +94,15 @@ int make_map(CUtensorMap* m, const void* base, int dtype, int D, int N, long lon
           chunk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FA2_OK : FA2_ERR_DRIVER;
+}
+
+// Context for one kernel launch.  Launches rotate through a ring of work counters (all zero
+// at module load, each left at zero by the kernel that used it), so kernels that overlap on
+// different streams do not share one.
+void make_ctx(DeviceState* d, LaunchCtx* ctx) {
+  ctx->status = d->status;
+  ctx->work_counter = d->counters + (d->next_counter.fetch_add(1) % kWorkCounterSlots);
+  ctx->num_sms = d->num_sms;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -138,8 +160,10 @@ int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   if (int e = make_map(&tv, v, dtype, D, N, BH, 128)) return e;
   if (int e = make_map(&to, o, dtype, D, N, BH, 32)) return e;
   const AttnShape s{B, H, N, D, dtype, scale};
-  return static_cast<int>(
-      launch_fwd(s, tq, tk, tv, to, lse, d->status, static_cast<cudaStream_t>(stream)));
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  LaunchCtx ctx;
+  make_ctx(d, &ctx);
+  return static_cast<int>(launch_fwd(s, tq, tk, tv, to, lse, ctx, st));
 }
 
 size_t fa2_rowstats_bytes(int B, int H, int N) {

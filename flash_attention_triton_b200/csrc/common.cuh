@@ -51,9 +51,31 @@ struct AttnShape {
   float scale;
 };
 
+// Per-launch context of the forward kernel.  It runs one CTA per SM; each CTA fetches work
+// items (pairs of Q tiles) from `work_counter` until none are left, so tensor memory is
+// allocated once and no SM idles between items.  The counter is zero before the launch and the kernel
+// leaves it at zero (see fetch_work_item), so no memset sits between launches.
+struct LaunchCtx {
+  int* status;                 // device status word (bounded-wait failures)
+  unsigned int* work_counter;  // device word, 0 at kernel start and again at kernel end
+  int num_sms;
+};
+
+// Next work item of this CTA (called by one thread).  With a counter, CTAs draw items in launch
+// order until the counter passes `total_items`; the launch draws total_items + gridDim.x numbers
+// in all, and whoever draws the last one puts the counter back to zero for the next launch that
+// uses it.  Without a counter every CTA handles the single item blockIdx.x.
+__device__ __forceinline__ int fetch_work_item(unsigned int* work_counter, int total_items,
+                                               bool first) {
+  if (work_counter == nullptr) return first ? static_cast<int>(blockIdx.x) : total_items;
+  const unsigned int next = atomicAdd(work_counter, 1u);
+  if (next == static_cast<unsigned int>(total_items) + gridDim.x - 1u) atomicExch(work_counter, 0u);
+  return next < static_cast<unsigned int>(total_items) ? static_cast<int>(next) : total_items;
+}
+
 cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const CUtensorMap& to, float* lse, int* status,
-                       cudaStream_t stream);
+                       const CUtensorMap& tv, const CUtensorMap& to, float* lse,
+                       const LaunchCtx& ctx, cudaStream_t stream);
 
 // rowstats[bh][t][0][r] = -lse * log2(e) (-inf for padded rows), rowstats[bh][t][1][r] = -delta.
 cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const void* dout,

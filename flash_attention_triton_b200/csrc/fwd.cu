@@ -59,7 +59,7 @@ struct FwdCfg {
   static constexpr int kBarPFull = kBarSFree + 2;    // 2: P_i written, O_i rescaled (4 arrivals)
   static constexpr int kBarPvDone = kBarPFull + 2;   // 2: O_i += P_i V completed
   static constexpr int kNumBars = kBarPvDone + 2;
-  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;  // + tmem slot, abort, work slot
   // tensor-memory columns
   static constexpr int kColS = 0;
   static constexpr int kColP = 128;  // P0 at 128, P1 at 192 (64 columns of 16-bit pairs each)
@@ -85,7 +85,8 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
     fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap to,
-               float* __restrict__ lse, int N, float scale_log2, int* status) {
+               float* __restrict__ lse, int N, int num_bh, float scale_log2, int* status,
+               unsigned int* work_counter) {
   using C = FwdCfg<D>;
   using T = Tile<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -96,7 +97,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   // still the tensor-memory lane quarter the hardware warp may access.
   const int warp = ((threadIdx.x >> 5) + 8) % 12;
   const int lane = threadIdx.x & 31;
-  FA2_CTA_TRACE(threadIdx.x == 0, 1);  // CTA entry
   const uint32_t smem_base = smem_u32(smem);
   if (smem_base & 1023u) {  // swizzled tiles need 1024-byte alignment
     if (threadIdx.x == 0) atomicCAS(status, 0, 0x20000 | kSiteAlign);
@@ -105,39 +105,14 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* work_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
   auto bar = [&](int i) { return smem_base + C::kOffBar + 8u * i; };
 
   const int ntiles = (N + 127) >> 7;
-  const int pair = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);  // heavy first
-  const int bh = blockIdx.y;
-  const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
-  const bool has1 = qt1 < ntiles;
-  const int n0 = qt0 + 1;             // KV tiles of Q tile 0
-  const int n1 = has1 ? qt1 + 1 : 0;  // KV tiles of Q tile 1 (one more than tile 0)
-  const int nkv = has1 ? n1 : n0;
-  const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
-  (void)traced;
+  const int npairs = (ntiles + 1) >> 1;
+  const int total_items = npairs * num_bh;
 
-  if (threadIdx.x == 0) {
-    mbar_init(bar(C::kBarQFull), 1);
-    for (int i = 0; i < C::kKStages; ++i) {
-      mbar_init(bar(C::kBarKFull + i), 1);
-      mbar_init(bar(C::kBarKEmpty + i), 1);
-    }
-    for (int i = 0; i < C::kVStages; ++i) {
-      mbar_init(bar(C::kBarVFull + i), 1);
-      mbar_init(bar(C::kBarVEmpty + i), 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(bar(C::kBarSFull + i), 1);
-      mbar_init(bar(C::kBarSFree + i), 4);
-      mbar_init(bar(C::kBarPFull + i), 4);
-      mbar_init(bar(C::kBarPvDone + i), 1);
-    }
-    *abort_flag = 0;
-    fence_mbar_init();
-    fence_proxy_async_smem();
-  }
+  if (threadIdx.x == 0) *abort_flag = 0;
   if (warp == 8) {
     tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
     tmem_relinquish();
@@ -147,7 +122,52 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const WaitCtx w{abort_flag, status};
-  FA2_CTA_TRACE(threadIdx.x == 0, 2);  // set-up done
+
+  // One CTA per SM; work items (one Q-tile pair of one (batch, head)) are fetched from a
+  // global counter in head-major, heavy-pair-first order, like a hardware block scheduler
+  // would hand them out, but without the launch gap and with tensor memory kept allocated.
+  // Between items all roles meet at a barrier and the mbarriers are re-initialised, so each
+  // item starts from phase 0.
+  for (bool first = true;; first = false) {
+    __syncthreads();  // every role has finished the previous item
+    if (threadIdx.x == 0) {
+      const int next = fetch_work_item(work_counter, total_items, first);
+      *work_slot = next;
+      if (next < total_items && !*abort_flag) {
+        if (!first)
+          for (int i = 0; i < C::kNumBars; ++i) mbar_inval(bar(i));
+        mbar_init(bar(C::kBarQFull), 1);
+        for (int i = 0; i < C::kKStages; ++i) {
+          mbar_init(bar(C::kBarKFull + i), 1);
+          mbar_init(bar(C::kBarKEmpty + i), 1);
+        }
+        for (int i = 0; i < C::kVStages; ++i) {
+          mbar_init(bar(C::kBarVFull + i), 1);
+          mbar_init(bar(C::kBarVEmpty + i), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+          mbar_init(bar(C::kBarSFull + i), 1);
+          mbar_init(bar(C::kBarSFree + i), 4);
+          mbar_init(bar(C::kBarPFull + i), 4);
+          mbar_init(bar(C::kBarPvDone + i), 1);
+        }
+        fence_mbar_init();
+        fence_proxy_async_smem();
+      }
+    }
+    __syncthreads();
+    const int item = *work_slot;
+    if (item >= total_items) break;
+    if (*abort_flag) continue;  // keep drawing so that the counter is left at zero
+    const int bh = item / npairs;
+    const int pair = npairs - 1 - (item - bh * npairs);  // heavy pairs of a head first
+    const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
+    const bool has1 = qt1 < ntiles;
+    const int n0 = qt0 + 1;             // KV tiles of Q tile 0
+    const int n1 = has1 ? qt1 + 1 : 0;  // KV tiles of Q tile 1 (one more than tile 0)
+    const int nkv = has1 ? n1 : n0;
+    const bool traced = item == 0;  // used by FA2_TRACE_EVENT only
+    (void)traced;
 
   if (warp >= 8) {
     reg_dec<72>();  // whole warpgroup (warps 8-11) gives registers to the softmax groups
@@ -272,7 +292,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     for (int j = 0; j < nj; ++j) {
       if (!(ok = mbar_wait_warp(bar(C::kBarSFull + wg), j & 1, w, kSiteSoftS))) break;
       tc_fence_after();
-      FA2_CTA_TRACE(j == 0 && warp == 0 && lane == 0, 3);  // first scores arrived
       FA2_TRACE_EVENT(traced && (warp & 3) == 0 && lane == 0, j * 16 + (wg ? 13 : 8));
       uint32_t sr[128];
       tmem_ld_x32(tS + 0, sr + 0);
@@ -354,10 +373,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
       l_run += (a01.x + a01.y) + (a23.x + a23.y);
     }
-    FA2_CTA_TRACE(warp == 0 && lane == 0, 4);  // main loop of group 0 done
     if (ok && nj > 0 && mbar_wait_warp(bar(C::kBarPvDone + wg), (nj - 1) & 1, w, kSiteSoftO)) {
       tc_fence_after();
-      FA2_CTA_TRACE(warp == 0 && lane == 0, 5);  // last O product done
       const float inv_l = 1.0f / l_run;
       // Stage the tile through the (now idle) Q buffer in the swizzled layout the output
       // tensor map expects; each warp stores its own 32 rows.
@@ -402,11 +419,11 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     }
   }
 
+  }  // work-item loop
+
   // ---------------------------------------------------------------------- teardown
-  FA2_CTA_TRACE(warp == 0 && lane == 0, 6);  // group 0 epilogue done
   tc_fence_before();
   __syncthreads();
-  FA2_CTA_TRACE(threadIdx.x == 0, 7);  // all roles done
   if (warp == 8) {
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
@@ -415,8 +432,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 
 template <int D, bool BF16>
 cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
-                         const CUtensorMap& tv, const CUtensorMap& to, float* lse, int* status,
-                         cudaStream_t stream) {
+                         const CUtensorMap& tv, const CUtensorMap& to, float* lse,
+                         const LaunchCtx& ctx, cudaStream_t stream) {
   using C = FwdCfg<D>;
   auto kern = fwd_kernel<D, BF16>;
   cudaError_t e =
@@ -424,9 +441,11 @@ cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtens
   if (e != cudaSuccess) return e;
   const int ntiles = (s.N + 127) / 128;
   const int npairs = (ntiles + 1) / 2;
-  dim3 grid(npairs, s.B * s.H);
+  const long long items = static_cast<long long>(npairs) * s.B * s.H;
+  const unsigned grid = static_cast<unsigned>(items < ctx.num_sms ? items : ctx.num_sms);
   const float scale_log2 = s.scale * 1.4426950408889634f;
-  kern<<<grid, kFwdThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, lse, s.N, scale_log2, status);
+  kern<<<grid, kFwdThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, lse, s.N, s.B * s.H,
+                                                     scale_log2, ctx.status, ctx.work_counter);
   return cudaGetLastError();
 }
 
@@ -436,18 +455,15 @@ cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtens
 extern "C" int fa2_trace_read_fwd(long long* out, int n) {
   return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n));
 }
-extern "C" int fa2_cta_trace_read_fwd(long long* out, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_cta_trace, sizeof(long long) * n));
-}
 #endif
 
 cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
-                       const CUtensorMap& tv, const CUtensorMap& to, float* lse, int* status,
-                       cudaStream_t stream) {
-#define FA2_CASE(DD)                                                                    \
-  case DD:                                                                              \
-    return s.dtype ? launch_fwd_t<DD, true>(s, tq, tk, tv, to, lse, status, stream)     \
-                   : launch_fwd_t<DD, false>(s, tq, tk, tv, to, lse, status, stream);
+                       const CUtensorMap& tv, const CUtensorMap& to, float* lse,
+                       const LaunchCtx& ctx, cudaStream_t stream) {
+#define FA2_CASE(DD)                                                                 \
+  case DD:                                                                           \
+    return s.dtype ? launch_fwd_t<DD, true>(s, tq, tk, tv, to, lse, ctx, stream)     \
+                   : launch_fwd_t<DD, false>(s, tq, tk, tv, to, lse, ctx, stream);
   switch (s.D) {
     FA2_CASE(32)
     FA2_CASE(64)

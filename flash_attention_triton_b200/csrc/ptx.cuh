@@ -29,6 +29,9 @@ struct WaitCtx {
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
+__device__ __forceinline__ void mbar_inval(uint32_t bar) {
+  asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -87,32 +90,26 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, co
 // per-translation-unit buffer that a fa2_trace_read_* entry point copies out.
 // ----------------------------------------------------------------------------------------
 #ifdef FA2_TRACE
-constexpr int kTraceSlots = 16384;
+constexpr int kTraceSlots = 32768;
 static __device__ long long g_trace[kTraceSlots];
 #define FA2_TRACE_EVENT(cond, slot)                                   \
   do {                                                                \
     if ((cond) && (slot) < fa2::kTraceSlots) fa2::g_trace[(slot)] = clock64(); \
   } while (0)
-// Per-CTA record (8 values per CTA): [0] SM id, [1..7] clock64 at points the kernel chooses.
-constexpr int kCtaTraceCtas = 8192;
-static __device__ long long g_cta_trace[kCtaTraceCtas * 8];
-__device__ __forceinline__ unsigned fa2_smid() {
-  unsigned r;
-  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
-  return r;
-}
-#define FA2_CTA_TRACE(cond, idx)                                                              \
-  do {                                                                                        \
-    const unsigned cta_ = blockIdx.y * gridDim.x + blockIdx.x;                                \
-    if ((cond) && cta_ < fa2::kCtaTraceCtas) {                                                \
-      fa2::g_cta_trace[cta_ * 8 + (idx)] = clock64();                                         \
-      if ((idx) == 1) fa2::g_cta_trace[cta_ * 8] = fa2::fa2_smid();                           \
-    }                                                                                         \
+// Same, storing the nanosecond globaltimer (to relate cycles to wall time).
+#define FA2_TRACE_TIME(cond, slot)                                    \
+  do {                                                                \
+    if ((cond) && (slot) < fa2::kTraceSlots) {                        \
+      long long t_;                                                   \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));          \
+      fa2::g_trace[(slot)] = t_;                                      \
+    }                                                                 \
   } while (0)
 #else
-#define FA2_CTA_TRACE(cond, idx) \
-  do {                           \
+#define FA2_TRACE_TIME(cond, slot) \
+  do {                             \
   } while (0)
+
 #define FA2_TRACE_EVENT(cond, slot) \
   do {                              \
   } while (0)
