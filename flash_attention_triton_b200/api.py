@@ -12,7 +12,9 @@ Mirrors ``src/flash_attention_triton/flash_attention_2.py`` of flash-attention-t
 
 Differences, all deliberate: fp16 and bf16 inputs run natively (the reference casts
 everything to fp16, lines 316/379); other float dtypes are cast to fp16 exactly as the
-reference does.  Head dimension must be 32, 64 or 128 and ``seqlen_q == seqlen_k``.
+reference does.  Head dimensions up to 128 are supported (multiples of 8 natively: the
+kernels run them zero-padded to 32 / 64 / 128 through TMA out-of-bounds fill; other sizes are
+zero-padded to a multiple of 8 on the host first) and ``seqlen_q == seqlen_k``.
 Everything runs through the C library on the tensors' CUDA device; there is no fallback.
 """
 
@@ -27,7 +29,7 @@ import torch
 
 from . import _lib
 
-_SUPPORTED_HEAD_DIMS = (32, 64, 128)
+_MAX_HEAD_DIM = 128
 
 
 # ------------------------------------------------------------------ host launch wrappers
@@ -58,8 +60,8 @@ def _flash_attention_forward(
     assert v.shape == (batch, nheads, seqlen_k, headdim)
     assert q.is_cuda and k.is_cuda and v.is_cuda, "All tensors must reside on CUDA device"
     assert q.dtype == k.dtype == v.dtype, "All tensors must be the same type"
-    if headdim not in _SUPPORTED_HEAD_DIMS:
-        raise ValueError(f"head dimension {headdim} is not supported (use one of {_SUPPORTED_HEAD_DIMS})")
+    if headdim > _MAX_HEAD_DIM or headdim % 8:
+        raise ValueError(f"head dimension {headdim} is not supported (multiples of 8 up to {_MAX_HEAD_DIM})")
     if seqlen_q != seqlen_k:
         raise ValueError("seqlen_q must equal seqlen_k (causal self-attention)")
     softmax_scale = softmax_scale or 1.0 / math.sqrt(headdim)
@@ -144,11 +146,19 @@ class FlashAttentionV2Function(torch.autograd.Function):
     def forward(ctx: Any, q, k, v, softmax_scale, deterministic):  # noqa: ANN001
         initial_dtype = q.dtype
         cdtype = _compute_dtype(q.dtype)
+        headdim = q.shape[-1]
+        if headdim > _MAX_HEAD_DIM:
+            raise ValueError(f"head dimension {headdim} is not supported (at most {_MAX_HEAD_DIM})")
+        softmax_scale = softmax_scale or 1.0 / math.sqrt(headdim)  # reference line 94: 0.0 -> default
         q, k, v = [t.contiguous().to(cdtype) for t in (q, k, v)]
+        pad = -headdim % 8  # zero columns change neither the scores nor the real output columns
+        if pad:
+            q, k, v = [torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v)]
         output, lse, ctx.softmax_scale = _flash_attention_forward(q, k, v, softmax_scale)
         ctx.save_for_backward(q, k, v, output, lse)
         ctx.deterministic = bool(deterministic)
-        return output.contiguous().to(initial_dtype)
+        ctx.headdim = headdim
+        return output[..., :headdim].contiguous().to(initial_dtype)
 
     @staticmethod
     def backward(ctx: Any, d_output):  # noqa: ANN001
@@ -156,10 +166,15 @@ class FlashAttentionV2Function(torch.autograd.Function):
         dq = torch.empty_like(q)
         dk = torch.empty_like(k)
         dv = torch.empty_like(v)
+        d_output = d_output.to(q.dtype)
+        pad = q.shape[-1] - ctx.headdim
+        if pad:
+            d_output = torch.nn.functional.pad(d_output, (0, pad))
         _flash_attention_backward(
-            q, k, v, output, lse, dq, dk, dv, d_output.to(q.dtype), ctx.softmax_scale,
-            ctx.deterministic,
+            q, k, v, output, lse, dq, dk, dv, d_output, ctx.softmax_scale, ctx.deterministic,
         )
+        if pad:
+            dq, dk, dv = [t[..., : ctx.headdim].contiguous() for t in (dq, dk, dv)]
         return dq, dk, dv, None, None
 
 

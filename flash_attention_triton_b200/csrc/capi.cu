@@ -76,12 +76,14 @@ int device_state(DeviceState** out) {
   return FA2_OK;
 }
 
-// Tensor map over a dense [BH, N, D] 16-bit tensor with box (chunk, box_rows, 1).
+// Tensor map over a dense [BH, N, D] 16-bit tensor with box (chunk, box_rows, 1).  The chunk
+// follows the padded head dim, so for D = 48 or 96 the last box of a row hangs over the
+// tensor: those columns read as zeros and are not written.
 int make_map(CUtensorMap* m, const void* base, int dtype, int D, int N, long long BH,
              int box_rows) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return FA2_ERR_DRIVER;
-  const int chunk = D >= 64 ? 64 : 32;
+  const int chunk = padded_head_dim(D) >= 64 ? 64 : 32;
   const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(N),
                               static_cast<cuuint64_t>(BH)};
   const cuuint64_t gstride[2] = {static_cast<cuuint64_t>(D) * 2,
@@ -108,12 +110,16 @@ void make_ctx(DeviceState* d, LaunchCtx* ctx) {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_shape(int B, int H, int N, int D, int dtype) {
-  if (D != 32 && D != 64 && D != 128) return FA2_ERR_HEAD_DIM;
+  if (D < 8 || D > 128 || D % 8 != 0) return FA2_ERR_HEAD_DIM;
   if (dtype != FA2_DTYPE_FP16 && dtype != FA2_DTYPE_BF16) return FA2_ERR_DTYPE;
   if (B <= 0 || H <= 0 || N <= 0) return FA2_ERR_SHAPE;
   if (static_cast<long long>(B) * H > 65535) return FA2_ERR_SHAPE;
   if (N > (1 << 24)) return FA2_ERR_SHAPE;
   return FA2_OK;
+}
+
+AttnShape make_shape(int B, int H, int N, int D, int dtype, float scale) {
+  return AttnShape{B, H, N, padded_head_dim(D), dtype, scale, D};
 }
 
 }  // namespace
@@ -129,7 +135,7 @@ const char* fa2_strerror(int code) {
   switch (code) {
     case FA2_OK: return "success";
     case FA2_ERR_NULL_POINTER: return "a required pointer is NULL";
-    case FA2_ERR_HEAD_DIM: return "head dimension must be 32, 64 or 128";
+    case FA2_ERR_HEAD_DIM: return "head dimension must be a multiple of 8 between 8 and 128";
     case FA2_ERR_DTYPE: return "dtype must be 0 (fp16) or 1 (bf16)";
     case FA2_ERR_MISALIGNED: return "tensor pointers must be 16-byte aligned";
     case FA2_ERR_SHAPE: return "B, H, N must be positive, B*H <= 65535, N <= 2^24";
@@ -159,7 +165,7 @@ int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
   if (int e = make_map(&tk, k, dtype, D, N, BH, 128)) return e;
   if (int e = make_map(&tv, v, dtype, D, N, BH, 128)) return e;
   if (int e = make_map(&to, o, dtype, D, N, BH, 32)) return e;
-  const AttnShape s{B, H, N, D, dtype, scale};
+  const AttnShape s = make_shape(B, H, N, D, dtype, scale);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   LaunchCtx ctx;
   make_ctx(d, &ctx);
@@ -179,7 +185,7 @@ int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float*
   if (!aligned16(o) || !aligned16(dout) || !aligned16(rowstats)) return FA2_ERR_MISALIGNED;
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
-  const AttnShape s{B, H, N, D, dtype, 1.f};
+  const AttnShape s = make_shape(B, H, N, D, dtype, 1.f);
   return static_cast<int>(
       launch_bwd_preprocess(s, o, dout, lse, rowstats, static_cast<cudaStream_t>(stream)));
 }
@@ -187,7 +193,7 @@ int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float*
 size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
   if (deterministic || B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
   const size_t ntiles = (static_cast<size_t>(N) + 127) / 128;
-  return static_cast<size_t>(B) * H * ntiles * 128 * D * sizeof(float);
+  return static_cast<size_t>(B) * H * ntiles * 128 * padded_head_dim(D) * sizeof(float);
 }
 
 int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const float* rowstats,
@@ -212,7 +218,7 @@ int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const
   if (int e = make_map(&tdo, dout, dtype, D, N, BH, 128)) return e;
   if (int e = make_map(&tdk, dk, dtype, D, N, BH, 32)) return e;
   if (int e = make_map(&tdv, dv, dtype, D, N, BH, 32)) return e;
-  const AttnShape s{B, H, N, D, dtype, scale};
+  const AttnShape s = make_shape(B, H, N, D, dtype, scale);
   if (deterministic) {
     if (int e = make_map(&tdq, dq, dtype, D, N, BH, 32)) return e;
     cudaError_t ce =
@@ -244,6 +250,7 @@ int fa2_selftest_mma(int form, const void* a, const void* b, float* c, int D, in
   if (!a || !b || !c) return FA2_ERR_NULL_POINTER;
   if (form < 0 || form > 2) return FA2_ERR_SHAPE;
   if (int e = check_shape(1, 1, 128, D, dtype)) return e;
+  if (D != padded_head_dim(D)) return FA2_ERR_HEAD_DIM;  // the self-test takes 32, 64, 128 only
   if (!aligned16(a) || !aligned16(b)) return FA2_ERR_MISALIGNED;
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;

@@ -46,10 +46,16 @@ __host__ __device__ __forceinline__ uint32_t swizzled_offset_128B(uint32_t row, 
 // Tensor maps describe [B*H, N, D] views: q/k/v/dout/o... with box (CH, 128, 1).
 // ----------------------------------------------------------------------------------------
 struct AttnShape {
-  int B, H, N, D;
+  int B, H, N;
+  int D;      // head dim the kernels are instantiated for: 32, 64 or 128
   int dtype;  // 0 = fp16, 1 = bf16
   float scale;
+  int Dg;     // head dim of the tensors in memory (a multiple of 8, <= D); the columns
+              // Dg..D-1 are zeros on TMA loads and dropped on TMA stores
 };
+
+// Smallest instantiated head dim that holds `d` columns.
+inline int padded_head_dim(int d) { return d <= 32 ? 32 : (d <= 64 ? 64 : 128); }
 
 // Per-launch context of the forward kernel.  It runs one CTA per SM; each CTA fetches work
 // items (pairs of Q tiles) from `work_counter` until none are left, so tensor memory is

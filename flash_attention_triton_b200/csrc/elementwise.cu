@@ -46,6 +46,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 
 // A group of D/8 adjacent lanes owns one row: each lane reads one 16-byte piece of o and of
 // dout, multiplies, and the group reduces with shuffles in a fixed order (deterministic).
+// D is the padded head dim; a row in memory has d8 <= D/8 pieces and the lanes beyond it
+// contribute zeros.
 // Rows are enumerated over the padded range [BH][T*128] so that the padding of rowstats is
 // written too (-lse2 = -inf makes every probability of a padded row exactly 0 downstream).
 // Both vectors are stored NEGATED so the consumers can use them as FMA / ADD addends directly.
@@ -53,7 +55,7 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kPreThreads)
     bwd_preprocess_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dout,
                           const float* __restrict__ lse, float* __restrict__ rowstats, int N,
-                          int npad, long long padded_rows) {
+                          int npad, long long padded_rows, int d8) {
   constexpr int kLanesPerRow = D / 8;
   constexpr int kRowsPerBlockPass = kPreThreads / kLanesPerRow;
   const int sub = threadIdx.x % kLanesPerRow;
@@ -68,9 +70,9 @@ __global__ void __launch_bounds__(kPreThreads)
     const long long bh = prow / npad;
     const int rr = static_cast<int>(prow - bh * npad);
     src_row[i] = (prow < padded_rows && rr < N) ? bh * N + rr : -1;
-    if (src_row[i] >= 0) {
-      a[i] = ld_stream(o + src_row[i] * kLanesPerRow + sub);
-      b[i] = ld_stream(dout + src_row[i] * kLanesPerRow + sub);
+    if (src_row[i] >= 0 && sub < d8) {
+      a[i] = ld_stream(o + src_row[i] * d8 + sub);
+      b[i] = ld_stream(dout + src_row[i] * d8 + sub);
     } else {
       a[i] = make_uint4(0, 0, 0, 0);
       b[i] = make_uint4(0, 0, 0, 0);
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(kPreThreads)
 template <int D, bool BF16>
 __global__ void __launch_bounds__(256)
     dq_convert_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, int N, int ntiles,
-                      long long total) {
+                      long long total, int d8) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   // idx = ((tile_global * 4 + w) * (D/8) + k8) * 32 + lane
@@ -113,7 +115,7 @@ __global__ void __launch_bounds__(256)
   const long long bh = tile_global / ntiles;
   const int tile = static_cast<int>(tile_global - bh * ntiles);
   const int row = tile * 128 + w * 32 + lane;
-  if (row >= N) return;
+  if (row >= N || k8 >= d8) return;  // padding rows / padding columns of the accumulator
   const long long blk = (tile_global * 4 + w) * (D / 4);  // in units of [32 lanes][float4]
   const float4 x = acc[(blk + 2 * k8) * 32 + lane];
   const float4 y = acc[(blk + 2 * k8 + 1) * 32 + lane];
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(256)
   r.y = pack2<BF16>(x.z, x.w);
   r.z = pack2<BF16>(y.x, y.y);
   r.w = pack2<BF16>(y.z, y.w);
-  dq[(bh * N + row) * (D / 8) + k8] = r;
+  dq[(bh * N + row) * d8 + k8] = r;
 }
 
 template <int D, bool BF16>
@@ -135,7 +137,7 @@ cudaError_t launch_pre_t(const AttnShape& s, const void* o, const void* dout, co
   const long long blocks = (padded_rows + kRowsPerBlock - 1) / kRowsPerBlock;
   bwd_preprocess_kernel<D, BF16><<<static_cast<unsigned>(blocks), kPreThreads, 0, stream>>>(
       static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, s.N, npad,
-      padded_rows);
+      padded_rows, s.Dg / 8);
   return cudaGetLastError();
 }
 
@@ -146,7 +148,8 @@ cudaError_t launch_cvt_t(const AttnShape& s, const float* dq_accum, void* dq,
   const long long total = static_cast<long long>(s.B) * s.H * ntiles * 128 * (D / 8);
   const long long blocks = (total + 255) / 256;
   dq_convert_kernel<D, BF16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
-      reinterpret_cast<const float4*>(dq_accum), static_cast<uint4*>(dq), s.N, ntiles, total);
+      reinterpret_cast<const float4*>(dq_accum), static_cast<uint4*>(dq), s.N, ntiles, total,
+      s.Dg / 8);
   return cudaGetLastError();
 }
 

@@ -40,7 +40,7 @@ def test_abi_version_and_error_text():
     lib = _lib.lib()
     assert lib.fa2_abi_version() == 1
     assert lib.fa2_strerror(0) == b"success"
-    assert b"32, 64 or 128" in lib.fa2_strerror(-2)
+    assert b"multiple of 8" in lib.fa2_strerror(-2)
     assert lib.fa2_strerror(-12345) == b"unknown fa2 error code"
 
 
@@ -52,13 +52,17 @@ def test_size_queries():
     # dq workspace: fp32 [B*H][ceil(N/128)*128][D], none in deterministic mode
     assert lib.fa2_bwd_workspace_bytes(2, 3, 4095, 32, 0) == 2 * 3 * 4096 * 32 * 4
     assert lib.fa2_bwd_workspace_bytes(2, 3, 4095, 32, 1) == 0
+    # head dims between the instantiated sizes accumulate in the next size up
+    assert lib.fa2_bwd_workspace_bytes(1, 1, 128, 48, 0) == 128 * 64 * 4
+    assert lib.fa2_bwd_workspace_bytes(1, 1, 128, 96, 0) == 128 * 128 * 4
 
 
 @pytest.mark.parametrize(
     "kwargs, code",
     [
         (dict(q=0), -1),                      # NULL pointer
-        (dict(D=48), -2),                     # unsupported head dim
+        (dict(D=44), -2),                     # head dim not a multiple of 8
+        (dict(D=136), -2),                    # head dim above 128
         (dict(dtype=7), -3),                  # unsupported dtype
         (dict(q=0x1008), -4),                 # misaligned pointer
         (dict(N=0), -5),                      # empty sequence
@@ -86,7 +90,7 @@ def test_backward_argument_errors_need_no_gpu():
     assert rc == -1
     rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], None, 1, 1, 128, 64, 0, None)
     assert rc == -1
-    rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], p[3], 1, 1, 128, 96, 0, None)
+    rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], p[3], 1, 1, 128, 256, 0, None)
     assert rc == -2
 
 

@@ -64,6 +64,13 @@ CASES = [
     ((1, 2, 1024, 128), torch.bfloat16, None, 1.0),
     ((1, 2, 2048, 128), torch.float16, None, 1.0),
     ((2, 3, 1023, 32), torch.float16, 0.5, 3.0),
+    # head dims between the instantiated 32 / 64 / 128 (the reference's own test shapes use 48
+    # and 96, tests/test_flash_attention_2.py:23-29) and one that is not a multiple of 8
+    ((2, 2, 1024, 48), torch.float16, None, 1.0),
+    ((1, 3, 1000, 96), torch.bfloat16, None, 1.0),
+    ((1, 2, 300, 8), torch.float16, None, 1.0),
+    ((1, 2, 333, 72), torch.float16, None, 1.0),
+    ((1, 2, 200, 20), torch.float16, None, 1.0),
     ((1, 2, 1, 64), torch.float16, None, 1.0),
     ((1, 2, 7, 32), torch.bfloat16, None, 1.0),
     ((1, 1, 127, 128), torch.bfloat16, None, 1.0),
@@ -133,7 +140,7 @@ def test_non_contiguous_inputs_are_accepted():
 
 
 def test_unsupported_head_dim_and_seqlen_mismatch_raise():
-    q = torch.randn(1, 1, 64, 48, device=DEV, dtype=torch.float16)
+    q = torch.randn(1, 1, 64, 160, device=DEV, dtype=torch.float16)
     with pytest.raises(ValueError, match="head dimension"):
         flash_attention_v2(q, q, q)
     q = torch.randn(1, 1, 64, 64, device=DEV, dtype=torch.float16)
@@ -188,6 +195,25 @@ def test_deterministic_mode_is_bit_identical_across_partitionings():
                 parts[key].append(r[key])
         for key in full:
             assert torch.equal(torch.cat(parts[key], dim=1).view_as(full[key]), full[key]), (key, world)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_deterministic_mode_is_bit_identical_across_gpus():
+    """Each GPU of the node computes its slab of (batch, head) problems; gathered, the results
+    equal the single-GPU results bit for bit (no collective on the data path)."""
+    world = min(torch.cuda.device_count(), 8)
+    q, k, v, do = make_inputs((2, 8, 1100, 128), torch.bfloat16)
+    full = run_api(q, k, v, do, None, True)
+    parts = {key: [] for key in full}
+    for rank in range(world):
+        dev = torch.device("cuda", rank)
+        sl = [shard_slab(t, world, rank) for t in (q, k, v, do)]
+        with torch.cuda.device(dev):
+            r = run_api(*sl, None, True, dev=dev)
+        for key in full:
+            parts[key].append(r[key].to(DEV))
+    for key in full:
+        assert torch.equal(torch.cat(parts[key], dim=1).view_as(full[key]), full[key]), key
 
 
 def test_atomic_mode_matches_deterministic_mode_closely():
