@@ -45,6 +45,24 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+def _readable_in_place(t: torch.Tensor) -> bool:
+    """Whether the kernels can read a ``[B, H, N, D]`` tensor through its own strides: unit
+    last stride, 16-byte aligned base, batch / head / row strides that are positive multiples
+    of 8 elements (strides of size-1 dimensions do not matter)."""
+    if t.stride(-1) != 1 or t.data_ptr() % 16:
+        return False
+    for size, stride in zip(t.shape[:3], t.stride()[:3]):
+        if size > 1 and (stride <= 0 or stride % 8):
+            return False
+    return t.shape[2] == 1 or t.stride(2) >= t.shape[3]
+
+
+def _as_kernel_input(t: torch.Tensor) -> torch.Tensor:
+    """The tensor itself when it can be read in place (e.g. a transposed ``[B, N, H, D]``
+    buffer), else a contiguous copy (what the reference always makes, line 316)."""
+    return t if _readable_in_place(t) else t.contiguous()
+
+
 def _flash_attention_forward(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, softmax_scale: float | None
 ) -> tuple[torch.Tensor, torch.Tensor, float]:
@@ -65,15 +83,16 @@ def _flash_attention_forward(
     if seqlen_q != seqlen_k:
         raise ValueError("seqlen_q must equal seqlen_k (causal self-attention)")
     softmax_scale = softmax_scale or 1.0 / math.sqrt(headdim)
-    output = torch.empty_like(q)
+    q, k, v = [_as_kernel_input(t) for t in (q, k, v)]
+    output = torch.empty(q.shape, device=q.device, dtype=q.dtype)  # dense, like the reference's O
     lse = torch.empty((batch, nheads, seqlen_q), device=q.device, dtype=torch.float32)
     with torch.cuda.device(q.device):
         _lib.check(
-            "fa2_fwd",
-            _lib.lib().fa2_fwd(
+            "fa2_fwd_strided",
+            _lib.lib().fa2_fwd_strided(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(), lse.data_ptr(),
                 batch, nheads, seqlen_q, headdim, _dtype_code(q.dtype), float(softmax_scale),
-                _stream(q),
+                _lib.stride_array(q, k, v, output), _stream(q),
             ),
         )
     return output, lse, softmax_scale
@@ -99,10 +118,11 @@ def _flash_attention_backward(
     writes dQ once, already rounded.
     """
     batch, nheads, seqlen_q, headdim = q.shape
-    if not d_output.is_contiguous():
-        d_output = d_output.contiguous()
+    # The reference requires everything contiguous here (lines 183-192) and copies dO when it
+    # is not (170-171); the inputs may keep their strides, only our own buffers are dense.
+    q, k, v, d_output = [_as_kernel_input(t) for t in (q, k, v, d_output)]
     assert lse.shape == (batch, nheads, seqlen_q)
-    assert q.is_contiguous() and k.is_contiguous() and v.is_contiguous() and output.is_contiguous()
+    assert output.is_contiguous()
     assert dq.is_contiguous() and dk.is_contiguous() and dv.is_contiguous()
     lib = _lib.lib()
     code = _dtype_code(q.dtype)
@@ -110,10 +130,11 @@ def _flash_attention_backward(
         stats_bytes = lib.fa2_rowstats_bytes(batch, nheads, seqlen_q)
         rowstats = torch.empty(stats_bytes // 4, device=q.device, dtype=torch.float32)
         _lib.check(
-            "fa2_bwd_preprocess",
-            lib.fa2_bwd_preprocess(
+            "fa2_bwd_preprocess_strided",
+            lib.fa2_bwd_preprocess_strided(
                 output.data_ptr(), d_output.data_ptr(), lse.data_ptr(), rowstats.data_ptr(),
-                batch, nheads, seqlen_q, headdim, code, _stream(q),
+                batch, nheads, seqlen_q, headdim, code, _lib.stride_array(output, d_output),
+                _stream(q),
             ),
         )
         ws_bytes = lib.fa2_bwd_workspace_bytes(batch, nheads, seqlen_q, headdim, int(deterministic))
@@ -121,13 +142,13 @@ def _flash_attention_backward(
             torch.empty(ws_bytes // 4, device=q.device, dtype=torch.float32) if ws_bytes else None
         )
         _lib.check(
-            "fa2_bwd",
-            lib.fa2_bwd(
+            "fa2_bwd_strided",
+            lib.fa2_bwd_strided(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), d_output.data_ptr(), rowstats.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                 dq_accum.data_ptr() if dq_accum is not None else None,
                 batch, nheads, seqlen_q, headdim, code, float(softmax_scale), int(deterministic),
-                _stream(q),
+                _lib.stride_array(q, k, v, d_output, dq, dk, dv), _stream(q),
             ),
         )
 
@@ -150,7 +171,7 @@ class FlashAttentionV2Function(torch.autograd.Function):
         if headdim > _MAX_HEAD_DIM:
             raise ValueError(f"head dimension {headdim} is not supported (at most {_MAX_HEAD_DIM})")
         softmax_scale = softmax_scale or 1.0 / math.sqrt(headdim)  # reference line 94: 0.0 -> default
-        q, k, v = [t.contiguous().to(cdtype) for t in (q, k, v)]
+        q, k, v = [_as_kernel_input(t.to(cdtype)) for t in (q, k, v)]
         pad = -headdim % 8  # zero columns change neither the scores nor the real output columns
         if pad:
             q, k, v = [torch.nn.functional.pad(t, (0, pad)) for t in (q, k, v)]
@@ -163,9 +184,7 @@ class FlashAttentionV2Function(torch.autograd.Function):
     @staticmethod
     def backward(ctx: Any, d_output):  # noqa: ANN001
         q, k, v, output, lse = ctx.saved_tensors
-        dq = torch.empty_like(q)
-        dk = torch.empty_like(k)
-        dv = torch.empty_like(v)
+        dq, dk, dv = (torch.empty(t.shape, device=t.device, dtype=t.dtype) for t in (q, k, v))
         d_output = d_output.to(q.dtype)
         pad = q.shape[-1] - ctx.headdim
         if pad:

@@ -59,7 +59,7 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
 template <int D, bool BF16>
 __device__ __forceinline__ void store_rows_16bit(uint32_t tmem_row_addr, uint8_t* stage, int warp4,
                                                  int lane, const CUtensorMap* map, int row_base,
-                                                 int bh, int N) {
+                                                 HeadCoord hc, int N) {
   using T = Tile<D>;
   const int r = warp4 * 32 + lane;
 #pragma unroll
@@ -84,7 +84,7 @@ __device__ __forceinline__ void store_rows_16bit(uint32_t tmem_row_addr, uint8_t
   __syncwarp();
   if (lane == 0 && row_base + warp4 * 32 < N) {
     for (int ch = 0; ch < T::kChunks; ++ch)
-      tma_store_3d(map, ch * T::kChunkElems, row_base + warp4 * 32, bh,
+      tma_store_4d(map, ch * T::kChunkElems, row_base + warp4 * 32, hc,
                    smem_u32(stage + ch * T::kChunkTileBytes + warp4 * 32 * T::kRowBytes));
     tma_store_commit();
     tma_store_wait_all();
@@ -174,7 +174,8 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
 
   const int ntiles = (N + 127) >> 7;
   const int jt = blockIdx.x;  // KV tile; tile 0 has the most Q tiles and is scheduled first
-  const int bh = blockIdx.y;
+  const HeadCoord hc{static_cast<int>(blockIdx.y), static_cast<int>(blockIdx.z)};  // grid (tiles, H, B)
+  const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
   const int nq = ntiles - jt;  // Q tiles jt .. ntiles-1
   const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
   (void)traced;
@@ -221,10 +222,10 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
         prefetch_tensormap(&tdo);
         mbar_arrive_expect_tx(bar(C::kBarKV), 2 * T::kTileBytes);
         for (int ch = 0; ch < T::kChunks; ++ch) {
-          tma_load_3d(smem_base + C::kOffK + ch * T::kChunkTileBytes, &tk, ch * T::kChunkElems,
-                      jt * 128, bh, bar(C::kBarKV));
-          tma_load_3d(smem_base + C::kOffV + ch * T::kChunkTileBytes, &tv, ch * T::kChunkElems,
-                      jt * 128, bh, bar(C::kBarKV));
+          tma_load_4d(smem_base + C::kOffK + ch * T::kChunkTileBytes, &tk, ch * T::kChunkElems,
+                      jt * 128, hc, bar(C::kBarKV));
+          tma_load_4d(smem_base + C::kOffV + ch * T::kChunkTileBytes, &tv, ch * T::kChunkElems,
+                      jt * 128, hc, bar(C::kBarKV));
         }
       }
       for (int ii = 0; ii < nq; ++ii) {
@@ -235,8 +236,8 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
           mbar_arrive_expect_tx(bar(C::kBarQFull + s), T::kTileBytes + 1024);
 #pragma unroll
           for (int ch = 0; ch < T::kChunks; ++ch)
-            tma_load_3d(smem_base + C::kOffQ + s * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
-                        ch * T::kChunkElems, qt * 128, bh, bar(C::kBarQFull + s));
+            tma_load_4d(smem_base + C::kOffQ + s * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
+                        ch * T::kChunkElems, qt * 128, hc, bar(C::kBarQFull + s));
           bulk_load_1d(smem_base + C::kOffStats + s * 1024,
                        rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024,
                        bar(C::kBarQFull + s));
@@ -246,8 +247,8 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
           mbar_arrive_expect_tx(bar(C::kBarDOFull + s), T::kTileBytes);
 #pragma unroll
           for (int ch = 0; ch < T::kChunks; ++ch)
-            tma_load_3d(smem_base + C::kOffDO + s * T::kTileBytes + ch * T::kChunkTileBytes, &tdo,
-                        ch * T::kChunkElems, qt * 128, bh, bar(C::kBarDOFull + s));
+            tma_load_4d(smem_base + C::kOffDO + s * T::kTileBytes + ch * T::kChunkTileBytes, &tdo,
+                        ch * T::kChunkElems, qt * 128, hc, bar(C::kBarDOFull + s));
         }
       }
     } else if (warp == C::kMmaWarp || warp == C::kMmaWarp + 2) {
@@ -476,10 +477,10 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
       tc_fence_after();
       if (wg == 0)
         store_rows_16bit<D, BF16>(tmem_base + lane_base + C::kColDV, smem + C::kOffDO, w4, lane,
-                                  &tdv, jt * 128, bh, N);
+                                  &tdv, jt * 128, hc, N);
       else
         store_rows_16bit<D, BF16>(tmem_base + lane_base + C::kColDK, smem + C::kOffQ, w4, lane,
-                                  &tdk, jt * 128, bh, N);
+                                  &tdk, jt * 128, hc, N);
     }
   }
 
@@ -556,7 +557,8 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
 
   const int ntiles = (N + 127) >> 7;
   const int qt = ntiles - 1 - static_cast<int>(blockIdx.x);  // heaviest Q tile first
-  const int bh = blockIdx.y;
+  const HeadCoord hc{static_cast<int>(blockIdx.y), static_cast<int>(blockIdx.z)};  // grid (tiles, H, B)
+  const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
   const int nkv = qt + 1;
   const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
   (void)traced;
@@ -604,10 +606,10 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
         prefetch_tensormap(&tdo);
         mbar_arrive_expect_tx(bar(C::kBarQ), 2 * T::kTileBytes + 1024);
         for (int ch = 0; ch < T::kChunks; ++ch) {
-          tma_load_3d(smem_base + C::kOffQ + ch * T::kChunkTileBytes, &tq, ch * T::kChunkElems,
-                      qt * 128, bh, bar(C::kBarQ));
-          tma_load_3d(smem_base + C::kOffDO + ch * T::kChunkTileBytes, &tdo, ch * T::kChunkElems,
-                      qt * 128, bh, bar(C::kBarQ));
+          tma_load_4d(smem_base + C::kOffQ + ch * T::kChunkTileBytes, &tq, ch * T::kChunkElems,
+                      qt * 128, hc, bar(C::kBarQ));
+          tma_load_4d(smem_base + C::kOffDO + ch * T::kChunkTileBytes, &tdo, ch * T::kChunkElems,
+                      qt * 128, hc, bar(C::kBarQ));
         }
         bulk_load_1d(smem_base + C::kOffStats,
                      rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024, bar(C::kBarQ));
@@ -619,8 +621,8 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
           mbar_arrive_expect_tx(bar(C::kBarKFull + ks), T::kTileBytes);
 #pragma unroll
           for (int ch = 0; ch < T::kChunks; ++ch)
-            tma_load_3d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
-                        ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + ks));
+            tma_load_4d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
+                        ch * T::kChunkElems, j * 128, hc, bar(C::kBarKFull + ks));
         }
         const int vs = j % C::kVStages, vph = (j / C::kVStages) & 1;
         if (!mbar_wait_warp(bar(C::kBarVEmpty + vs), vph ^ 1, w, kBSiteLoadDO)) break;
@@ -628,8 +630,8 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
           mbar_arrive_expect_tx(bar(C::kBarVFull + vs), T::kTileBytes);
 #pragma unroll
           for (int ch = 0; ch < T::kChunks; ++ch)
-            tma_load_3d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
-                        ch * T::kChunkElems, j * 128, bh, bar(C::kBarVFull + vs));
+            tma_load_4d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
+                        ch * T::kChunkElems, j * 128, hc, bar(C::kBarVFull + vs));
         }
       }
     } else if (warp == C::kMmaWarp) {
@@ -786,7 +788,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
     if (ok && wg == 0 && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
       tc_fence_after();
       store_rows_16bit<D, BF16>(tmem_base + lane_base + C::kColDQ, smem + C::kOffDO, w4, lane, &tdq,
-                                qt * 128, bh, N);
+                                qt * 128, hc, N);
     }
   }
 
@@ -809,7 +811,7 @@ cudaError_t launch_dkdv_t(const AttnShape& s, const CUtensorMap& tq, const CUten
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int ntiles = (s.N + 127) / 128;
-  dim3 grid(ntiles, s.B * s.H);
+  dim3 grid(ntiles, s.H, s.B);
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum,
                                                      s.N, s.scale, s.scale * 1.4426950408889634f,
                                                      status);
@@ -826,7 +828,7 @@ cudaError_t launch_dq_t(const AttnShape& s, const CUtensorMap& tq, const CUtenso
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int ntiles = (s.N + 127) / 128;
-  dim3 grid(ntiles, s.B * s.H);
+  dim3 grid(ntiles, s.H, s.B);
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, rowstats, s.N, s.scale,
                                                      s.scale * 1.4426950408889634f, status);
   return cudaGetLastError();

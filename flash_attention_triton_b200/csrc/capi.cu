@@ -76,26 +76,55 @@ int device_state(DeviceState** out) {
   return FA2_OK;
 }
 
-// Tensor map over a dense [BH, N, D] 16-bit tensor with box (chunk, box_rows, 1).  The chunk
+// Strides of tensor `idx` of a call: the caller's triple, or dense when the array is NULL or
+// the triple is all zeros.  Strides of size-1 dimensions carry no information (frameworks
+// put anything there) and are replaced by the dense ones.
+int get_strides(const long long* user, int idx, int B, int H, int N, int D, Strides* out) {
+  const Strides dense{static_cast<long long>(H) * N * D, static_cast<long long>(N) * D, D};
+  *out = dense;
+  if (!user) return FA2_OK;
+  const long long* u = user + 3 * idx;
+  if (u[0] == 0 && u[1] == 0 && u[2] == 0) return FA2_OK;
+  if (B > 1) out->b = u[0];
+  if (H > 1) out->h = u[1];
+  if (N > 1) out->n = u[2];
+  const long long v[3] = {out->b, out->h, out->n};
+  for (long long x : v)
+    if (x <= 0 || x % 8 != 0 || x >= (1ll << 38)) return FA2_ERR_STRIDE;
+  if (out->n < D) return FA2_ERR_STRIDE;
+  return FA2_OK;
+}
+
+// Tensor map over a [B, H, N, D] 16-bit tensor with box (chunk, box_rows, 1, 1).  The chunk
 // follows the padded head dim, so for D = 48 or 96 the last box of a row hangs over the
 // tensor: those columns read as zeros and are not written.
-int make_map(CUtensorMap* m, const void* base, int dtype, int D, int N, long long BH,
-             int box_rows) {
+int make_map(CUtensorMap* m, const void* base, int dtype, int B, int H, int N, int D,
+             const Strides& st, int box_rows) {
   EncodeTiledFn enc = get_encode();
   if (!enc) return FA2_ERR_DRIVER;
   const int chunk = padded_head_dim(D) >= 64 ? 64 : 32;
-  const cuuint64_t gdim[3] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(N),
-                              static_cast<cuuint64_t>(BH)};
-  const cuuint64_t gstride[2] = {static_cast<cuuint64_t>(D) * 2,
-                                 static_cast<cuuint64_t>(N) * D * 2};
-  const cuuint32_t box[3] = {static_cast<cuuint32_t>(chunk), static_cast<cuuint32_t>(box_rows), 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
+  const cuuint64_t gdim[4] = {static_cast<cuuint64_t>(D), static_cast<cuuint64_t>(N),
+                              static_cast<cuuint64_t>(H), static_cast<cuuint64_t>(B)};
+  const cuuint64_t gstride[3] = {static_cast<cuuint64_t>(st.n) * 2,
+                                 static_cast<cuuint64_t>(st.h) * 2,
+                                 static_cast<cuuint64_t>(st.b) * 2};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(chunk), static_cast<cuuint32_t>(box_rows), 1,
+                             1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
   const CUresult r =
-      enc(m, dtype ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+      enc(m, dtype ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
           const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
           chunk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FA2_OK : FA2_ERR_DRIVER;
+}
+
+// Map of tensor `idx` of a call (strides as get_strides resolves them).
+int make_map_of(CUtensorMap* m, const void* base, const long long* user, int idx, int dtype,
+                int B, int H, int N, int D, int box_rows) {
+  Strides st;
+  if (int e = get_strides(user, idx, B, H, N, D, &st)) return e;
+  return make_map(m, base, dtype, B, H, N, D, st, box_rows);
 }
 
 // Context for one kernel launch.  Launches rotate through a ring of work counters (all zero
@@ -144,6 +173,8 @@ const char* fa2_strerror(int code) {
     case FA2_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
     case FA2_ERR_SCALE: return "softmax scale must be finite and > 0";
     case FA2_ERR_WORKSPACE: return "dq_accum workspace is required when deterministic == 0";
+    case FA2_ERR_STRIDE:
+      return "strides must be positive multiples of 8 elements (16 bytes), row stride >= D";
     case FA2_ERR_TOO_LARGE: return "problem exceeds the built-in scratch (B*H*ceil(N/128) > 4096)";
     default: break;
   }
@@ -151,25 +182,34 @@ const char* fa2_strerror(int code) {
   return "unknown fa2 error code";
 }
 
-int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int N,
-            int D, int dtype, float scale, fa2_stream_t stream) {
+int fa2_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                    int N, int D, int dtype, float scale, const long long* strides,
+                    fa2_stream_t stream) {
   if (!q || !k || !v || !o || !lse) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return FA2_ERR_MISALIGNED;
   if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
+  for (int idx = 0; idx < 4; ++idx) {
+    Strides unused;
+    if (int e = get_strides(strides, idx, B, H, N, D, &unused)) return e;
+  }
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
-  const long long BH = static_cast<long long>(B) * H;
   CUtensorMap tq, tk, tv, to;
-  if (int e = make_map(&tq, q, dtype, D, N, BH, 128)) return e;
-  if (int e = make_map(&tk, k, dtype, D, N, BH, 128)) return e;
-  if (int e = make_map(&tv, v, dtype, D, N, BH, 128)) return e;
-  if (int e = make_map(&to, o, dtype, D, N, BH, 32)) return e;
+  if (int e = make_map_of(&tq, q, strides, 0, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&tk, k, strides, 1, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&tv, v, strides, 2, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&to, o, strides, 3, dtype, B, H, N, D, 32)) return e;
   const AttnShape s = make_shape(B, H, N, D, dtype, scale);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   LaunchCtx ctx;
   make_ctx(d, &ctx);
   return static_cast<int>(launch_fwd(s, tq, tk, tv, to, lse, ctx, st));
+}
+
+int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int N,
+            int D, int dtype, float scale, fa2_stream_t stream) {
+  return fa2_fwd_strided(q, k, v, o, lse, B, H, N, D, dtype, scale, nullptr, stream);
 }
 
 size_t fa2_rowstats_bytes(int B, int H, int N) {
@@ -178,16 +218,25 @@ size_t fa2_rowstats_bytes(int B, int H, int N) {
   return static_cast<size_t>(B) * H * ntiles * 256 * sizeof(float);
 }
 
-int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float* rowstats, int B,
-                       int H, int N, int D, int dtype, fa2_stream_t stream) {
+int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse, float* rowstats,
+                               int B, int H, int N, int D, int dtype, const long long* strides,
+                               fa2_stream_t stream) {
   if (!o || !dout || !lse || !rowstats) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
   if (!aligned16(o) || !aligned16(dout) || !aligned16(rowstats)) return FA2_ERR_MISALIGNED;
+  Strides so, sdo;
+  if (int e = get_strides(strides, 0, B, H, N, D, &so)) return e;
+  if (int e = get_strides(strides, 1, B, H, N, D, &sdo)) return e;
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
   const AttnShape s = make_shape(B, H, N, D, dtype, 1.f);
-  return static_cast<int>(
-      launch_bwd_preprocess(s, o, dout, lse, rowstats, static_cast<cudaStream_t>(stream)));
+  return static_cast<int>(launch_bwd_preprocess(s, o, so, dout, sdo, lse, rowstats,
+                                                static_cast<cudaStream_t>(stream)));
+}
+
+int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float* rowstats, int B,
+                       int H, int N, int D, int dtype, fa2_stream_t stream) {
+  return fa2_bwd_preprocess_strided(o, dout, lse, rowstats, B, H, N, D, dtype, nullptr, stream);
 }
 
 size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
@@ -196,9 +245,10 @@ size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
   return static_cast<size_t>(B) * H * ntiles * 128 * padded_head_dim(D) * sizeof(float);
 }
 
-int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const float* rowstats,
-            void* dq, void* dk, void* dv, float* dq_accum, int B, int H, int N, int D, int dtype,
-            float scale, int deterministic, fa2_stream_t stream) {
+int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dout,
+                    const float* rowstats, void* dq, void* dk, void* dv, float* dq_accum, int B,
+                    int H, int N, int D, int dtype, float scale, int deterministic,
+                    const long long* strides, fa2_stream_t stream) {
   if (!q || !k || !v || !dout || !rowstats || !dq || !dk || !dv) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(dout) || !aligned16(dq) ||
@@ -207,20 +257,25 @@ int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const
   if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
   if (!deterministic && !dq_accum) return FA2_ERR_WORKSPACE;
   if (!deterministic && !aligned16(dq_accum)) return FA2_ERR_MISALIGNED;
+  for (int idx = 0; idx < 7; ++idx) {
+    Strides unused;
+    if (int e = get_strides(strides, idx, B, H, N, D, &unused)) return e;
+  }
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
-  const long long BH = static_cast<long long>(B) * H;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
-  if (int e = make_map(&tq, q, dtype, D, N, BH, 128)) return e;
-  if (int e = make_map(&tk, k, dtype, D, N, BH, 128)) return e;
-  if (int e = make_map(&tv, v, dtype, D, N, BH, 128)) return e;
-  if (int e = make_map(&tdo, dout, dtype, D, N, BH, 128)) return e;
-  if (int e = make_map(&tdk, dk, dtype, D, N, BH, 32)) return e;
-  if (int e = make_map(&tdv, dv, dtype, D, N, BH, 32)) return e;
+  if (int e = make_map_of(&tq, q, strides, 0, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&tk, k, strides, 1, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&tv, v, strides, 2, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&tdo, dout, strides, 3, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&tdk, dk, strides, 5, dtype, B, H, N, D, 32)) return e;
+  if (int e = make_map_of(&tdv, dv, strides, 6, dtype, B, H, N, D, 32)) return e;
+  Strides sdq;
+  if (int e = get_strides(strides, 4, B, H, N, D, &sdq)) return e;
   const AttnShape s = make_shape(B, H, N, D, dtype, scale);
   if (deterministic) {
-    if (int e = make_map(&tdq, dq, dtype, D, N, BH, 32)) return e;
+    if (int e = make_map(&tdq, dq, dtype, B, H, N, D, sdq, 32)) return e;
     cudaError_t ce =
         launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, nullptr, 0, d->status, st);
     if (ce != cudaSuccess) return static_cast<int>(ce);
@@ -230,7 +285,14 @@ int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const
   if (ce != cudaSuccess) return static_cast<int>(ce);
   ce = launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum, 1, d->status, st);
   if (ce != cudaSuccess) return static_cast<int>(ce);
-  return static_cast<int>(launch_dq_convert(s, dq_accum, dq, st));
+  return static_cast<int>(launch_dq_convert(s, dq_accum, dq, sdq, st));
+}
+
+int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const float* rowstats,
+            void* dq, void* dk, void* dv, float* dq_accum, int B, int H, int N, int D, int dtype,
+            float scale, int deterministic, fa2_stream_t stream) {
+  return fa2_bwd_strided(q, k, v, dout, rowstats, dq, dk, dv, dq_accum, B, H, N, D, dtype, scale,
+                         deterministic, nullptr, stream);
 }
 
 int fa2_device_status(int* status_out) {
@@ -256,8 +318,8 @@ int fa2_selftest_mma(int form, const void* a, const void* b, float* c, int D, in
   if (int e = device_state(&d)) return e;
   CUtensorMap ta, tb;
   // form 0 reads A [128, D] through TMA; forms 1 and 2 read A [128, 128] with plain loads.
-  if (int e = make_map(&ta, form == 0 ? a : b, dtype, D, 128, 1, 128)) return e;
-  if (int e = make_map(&tb, b, dtype, D, 128, 1, 128)) return e;
+  if (int e = make_map_of(&ta, form == 0 ? a : b, nullptr, 0, dtype, 1, 1, 128, D, 128)) return e;
+  if (int e = make_map_of(&tb, b, nullptr, 0, dtype, 1, 1, 128, D, 128)) return e;
   return static_cast<int>(launch_selftest_mma(form, ta, tb, a, c, D, dtype, d->status,
                                               static_cast<cudaStream_t>(stream)));
 }

@@ -43,7 +43,7 @@ __host__ __device__ __forceinline__ uint32_t swizzled_offset_128B(uint32_t row, 
 
 // ----------------------------------------------------------------------------------------
 // Host launchers (one per kernel family), defined in the .cu files of this directory.
-// Tensor maps describe [B*H, N, D] views: q/k/v/dout/o... with box (CH, 128, 1).
+// Tensor maps describe [B, H, N, D] tensors with box (CH, 128 or 32, 1, 1).
 // ----------------------------------------------------------------------------------------
 struct AttnShape {
   int B, H, N;
@@ -52,6 +52,11 @@ struct AttnShape {
   float scale;
   int Dg;     // head dim of the tensors in memory (a multiple of 8, <= D); the columns
               // Dg..D-1 are zeros on TMA loads and dropped on TMA stores
+};
+
+// Element strides of one [B, H, N, D] tensor (the last dimension is contiguous).
+struct Strides {
+  long long b, h, n;
 };
 
 // Smallest instantiated head dim that holds `d` columns.
@@ -84,8 +89,9 @@ cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensor
                        const LaunchCtx& ctx, cudaStream_t stream);
 
 // rowstats[bh][t][0][r] = -lse * log2(e) (-inf for padded rows), rowstats[bh][t][1][r] = -delta.
-cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const void* dout,
-                                  const float* lse, float* rowstats, cudaStream_t stream);
+cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strides& so,
+                                  const void* dout, const Strides& sdo, const float* lse,
+                                  float* rowstats, cudaStream_t stream);
 
 // dK/dV per KV tile.  fuse_dq != 0 also accumulates dQ into dq_accum with fp32 atomic adds.
 // dq_accum layout: [bh][t][w = 4][k = D/4][lane = 32][4] floats, holding element
@@ -103,7 +109,7 @@ cudaError_t launch_bwd_dq(const AttnShape& s, const CUtensorMap& tq, const CUten
 
 // dq = convert(dq_accum) (non-deterministic path).
 cudaError_t launch_dq_convert(const AttnShape& s, const float* dq_accum, void* dq,
-                              cudaStream_t stream);
+                              const Strides& sdq, cudaStream_t stream);
 
 cudaError_t launch_selftest_mma(int form, const CUtensorMap& ta, const CUtensorMap& tb,
                                 const void* a_raw, float* c, int D, int dtype, int* status,

@@ -55,7 +55,8 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kPreThreads)
     bwd_preprocess_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dout,
                           const float* __restrict__ lse, float* __restrict__ rowstats, int N,
-                          int npad, long long padded_rows, int d8) {
+                          int npad, long long padded_rows, int d8, int H, Strides so,
+                          Strides sdo) {
   constexpr int kLanesPerRow = D / 8;
   constexpr int kRowsPerBlockPass = kPreThreads / kLanesPerRow;
   const int sub = threadIdx.x % kLanesPerRow;
@@ -71,8 +72,10 @@ __global__ void __launch_bounds__(kPreThreads)
     const int rr = static_cast<int>(prow - bh * npad);
     src_row[i] = (prow < padded_rows && rr < N) ? bh * N + rr : -1;
     if (src_row[i] >= 0 && sub < d8) {
-      a[i] = ld_stream(o + src_row[i] * d8 + sub);
-      b[i] = ld_stream(dout + src_row[i] * d8 + sub);
+      // strides are in 16-byte units (the host divides the element strides by 8)
+      const long long bb = bh / H, hh = bh - bb * H;
+      a[i] = ld_stream(o + bb * so.b + hh * so.h + rr * so.n + sub);
+      b[i] = ld_stream(dout + bb * sdo.b + hh * sdo.h + rr * sdo.n + sub);
     } else {
       a[i] = make_uint4(0, 0, 0, 0);
       b[i] = make_uint4(0, 0, 0, 0);
@@ -102,7 +105,7 @@ __global__ void __launch_bounds__(kPreThreads)
 template <int D, bool BF16>
 __global__ void __launch_bounds__(256)
     dq_convert_kernel(const float4* __restrict__ acc, uint4* __restrict__ dq, int N, int ntiles,
-                      long long total, int d8) {
+                      long long total, int d8, int H, Strides sdq) {
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   // idx = ((tile_global * 4 + w) * (D/8) + k8) * 32 + lane
@@ -124,12 +127,17 @@ __global__ void __launch_bounds__(256)
   r.y = pack2<BF16>(x.z, x.w);
   r.z = pack2<BF16>(y.x, y.y);
   r.w = pack2<BF16>(y.z, y.w);
-  dq[(bh * N + row) * d8 + k8] = r;
+  const long long bb = bh / H, hh = bh - bb * H;
+  dq[bb * sdq.b + hh * sdq.h + row * sdq.n + k8] = r;  // strides in 16-byte units
 }
 
+// Element strides -> strides in 16-byte pieces (every stride is a multiple of 8 elements).
+Strides in_vec8(const Strides& st) { return Strides{st.b / 8, st.h / 8, st.n / 8}; }
+
 template <int D, bool BF16>
-cudaError_t launch_pre_t(const AttnShape& s, const void* o, const void* dout, const float* lse,
-                         float* rowstats, cudaStream_t stream) {
+cudaError_t launch_pre_t(const AttnShape& s, const void* o, const Strides& so, const void* dout,
+                         const Strides& sdo, const float* lse, float* rowstats,
+                         cudaStream_t stream) {
   const int ntiles = (s.N + 127) / 128;
   const int npad = ntiles * 128;
   const long long padded_rows = static_cast<long long>(s.B) * s.H * npad;
@@ -137,30 +145,31 @@ cudaError_t launch_pre_t(const AttnShape& s, const void* o, const void* dout, co
   const long long blocks = (padded_rows + kRowsPerBlock - 1) / kRowsPerBlock;
   bwd_preprocess_kernel<D, BF16><<<static_cast<unsigned>(blocks), kPreThreads, 0, stream>>>(
       static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, s.N, npad,
-      padded_rows, s.Dg / 8);
+      padded_rows, s.Dg / 8, s.H, in_vec8(so), in_vec8(sdo));
   return cudaGetLastError();
 }
 
 template <int D, bool BF16>
-cudaError_t launch_cvt_t(const AttnShape& s, const float* dq_accum, void* dq,
+cudaError_t launch_cvt_t(const AttnShape& s, const float* dq_accum, void* dq, const Strides& sdq,
                          cudaStream_t stream) {
   const int ntiles = (s.N + 127) / 128;
   const long long total = static_cast<long long>(s.B) * s.H * ntiles * 128 * (D / 8);
   const long long blocks = (total + 255) / 256;
   dq_convert_kernel<D, BF16><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
       reinterpret_cast<const float4*>(dq_accum), static_cast<uint4*>(dq), s.N, ntiles, total,
-      s.Dg / 8);
+      s.Dg / 8, s.H, in_vec8(sdq));
   return cudaGetLastError();
 }
 
 }  // namespace
 
-cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const void* dout,
-                                  const float* lse, float* rowstats, cudaStream_t stream) {
+cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strides& so,
+                                  const void* dout, const Strides& sdo, const float* lse,
+                                  float* rowstats, cudaStream_t stream) {
 #define FA2_CASE(DD)                                                                 \
   case DD:                                                                           \
-    return s.dtype ? launch_pre_t<DD, true>(s, o, dout, lse, rowstats, stream)       \
-                   : launch_pre_t<DD, false>(s, o, dout, lse, rowstats, stream);
+    return s.dtype ? launch_pre_t<DD, true>(s, o, so, dout, sdo, lse, rowstats, stream)  \
+                   : launch_pre_t<DD, false>(s, o, so, dout, sdo, lse, rowstats, stream);
   switch (s.D) {
     FA2_CASE(32)
     FA2_CASE(64)
@@ -171,11 +180,11 @@ cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const void*
 }
 
 cudaError_t launch_dq_convert(const AttnShape& s, const float* dq_accum, void* dq,
-                              cudaStream_t stream) {
+                              const Strides& sdq, cudaStream_t stream) {
 #define FA2_CASE(DD)                                                        \
   case DD:                                                                  \
-    return s.dtype ? launch_cvt_t<DD, true>(s, dq_accum, dq, stream)        \
-                   : launch_cvt_t<DD, false>(s, dq_accum, dq, stream);
+    return s.dtype ? launch_cvt_t<DD, true>(s, dq_accum, dq, sdq, stream)   \
+                   : launch_cvt_t<DD, false>(s, dq_accum, dq, sdq, stream);
   switch (s.D) {
     FA2_CASE(32)
     FA2_CASE(64)

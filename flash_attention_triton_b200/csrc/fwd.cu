@@ -85,8 +85,8 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
     fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap to,
-               float* __restrict__ lse, int N, int num_bh, float scale_log2, int* status,
-               unsigned int* work_counter) {
+               float* __restrict__ lse, int N, int num_bh, int num_heads, float scale_log2,
+               int* status, unsigned int* work_counter) {
   using C = FwdCfg<D>;
   using T = Tile<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -160,6 +160,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     if (item >= total_items) break;
     if (*abort_flag) continue;  // keep drawing so that the counter is left at zero
     const int bh = item / npairs;
+    const HeadCoord hc{bh % num_heads, bh / num_heads};
     const int pair = npairs - 1 - (item - bh * npairs);  // heavy pairs of a head first
     const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
     const bool has1 = qt1 < ntiles;
@@ -182,8 +183,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         mbar_arrive_expect_tx(bar(C::kBarQFull), (has1 ? 2 : 1) * T::kTileBytes);
         for (int i = 0; i < (has1 ? 2 : 1); ++i)
           for (int ch = 0; ch < T::kChunks; ++ch)
-            tma_load_3d(smem_base + C::kOffQ + i * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
-                        ch * T::kChunkElems, (qt0 + i) * 128, bh, bar(C::kBarQFull));
+            tma_load_4d(smem_base + C::kOffQ + i * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
+                        ch * T::kChunkElems, (qt0 + i) * 128, hc, bar(C::kBarQFull));
       }
       // K runs one tile ahead of V: S(j+1) is issued during KV step j.
       for (int j = 0; j <= nkv; ++j) {
@@ -194,8 +195,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
             mbar_arrive_expect_tx(bar(C::kBarKFull + ks), T::kTileBytes);
 #pragma unroll
             for (int ch = 0; ch < T::kChunks; ++ch)
-              tma_load_3d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
-                          ch * T::kChunkElems, j * 128, bh, bar(C::kBarKFull + ks));
+              tma_load_4d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
+                          ch * T::kChunkElems, j * 128, hc, bar(C::kBarKFull + ks));
           }
         }
         if (j > 0) {
@@ -206,8 +207,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
             mbar_arrive_expect_tx(bar(C::kBarVFull + vs), T::kTileBytes);
 #pragma unroll
             for (int ch = 0; ch < T::kChunks; ++ch)
-              tma_load_3d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
-                          ch * T::kChunkElems, jv * 128, bh, bar(C::kBarVFull + vs));
+              tma_load_4d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
+                          ch * T::kChunkElems, jv * 128, hc, bar(C::kBarVFull + vs));
           }
         }
       }
@@ -407,7 +408,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         const int row0 = (warp & 3) * 32;
         if (qt * 128 + row0 < N) {
           for (int ch = 0; ch < T::kChunks; ++ch)
-            tma_store_3d(&to, ch * T::kChunkElems, qt * 128 + row0, bh,
+            tma_store_4d(&to, ch * T::kChunkElems, qt * 128 + row0, hc,
                          smem_u32(sO + ch * T::kChunkTileBytes + row0 * T::kRowBytes));
           tma_store_commit();
           tma_store_wait_all();
@@ -444,7 +445,7 @@ cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtens
   const long long items = static_cast<long long>(npairs) * s.B * s.H;
   const unsigned grid = static_cast<unsigned>(items < ctx.num_sms ? items : ctx.num_sms);
   const float scale_log2 = s.scale * 1.4426950408889634f;
-  kern<<<grid, kFwdThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, lse, s.N, s.B * s.H,
+  kern<<<grid, kFwdThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, lse, s.N, s.B * s.H, s.H,
                                                      scale_log2, ctx.status, ctx.work_counter);
   return cudaGetLastError();
 }

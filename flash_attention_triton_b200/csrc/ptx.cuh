@@ -126,22 +126,27 @@ __device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t nthreads) {
 }
 
 // ----------------------------------------------------------------------------------------
-// TMA: tiled 3-D tensor copies, coordinates {x = element in row, y = row, z = batch*head}
+// TMA: tiled 4-D tensor copies, coordinates {x = element in row, y = row, head, batch}.
+// Batch and head are separate dimensions so that the tensors may have any batch / head /
+// row strides (multiples of 16 bytes); boxes are always one head of one batch wide.
 // ----------------------------------------------------------------------------------------
-__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map, int x,
-                                            int y, int z, uint32_t bar) {
+struct HeadCoord {
+  int h, b;
+};
+__device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const CUtensorMap* map, int x,
+                                            int y, HeadCoord hc, uint32_t bar) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
-      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
-      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(dst_smem),
+      "l"(map), "r"(x), "r"(y), "r"(hc.h), "r"(hc.b), "r"(bar)
       : "memory");
 }
-__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z,
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, int x, int y, HeadCoord hc,
                                              uint32_t src_smem) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(
-          map),
-      "r"(x), "r"(y), "r"(z), "r"(src_smem)
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3, %4}], [%5];" ::
+          "l"(map),
+      "r"(x), "r"(y), "r"(hc.h), "r"(hc.b), "r"(src_smem)
       : "memory");
 }
 __device__ __forceinline__ void tma_store_commit() {

@@ -92,9 +92,8 @@ __global__ void __launch_bounds__(kSelfThreads, 1)
     mbar_arrive_expect_tx(bar_load, bytes);
     for (int ch = 0; ch < T::kChunks; ++ch) {
       if (form == 0)
-        tma_load_3d(smem_base + C::kOffA + ch * T::kChunkTileBytes, &ta, ch * T::kChunkElems, 0,
-                    0, bar_load);
-      tma_load_3d(smem_base + C::kOffB + ch * T::kChunkTileBytes, &tb, ch * T::kChunkElems, 0, 0,
+        tma_load_4d(smem_base + C::kOffA + ch * T::kChunkTileBytes, &ta, ch * T::kChunkElems, 0, HeadCoord{0, 0}, bar_load);
+      tma_load_4d(smem_base + C::kOffB + ch * T::kChunkTileBytes, &tb, ch * T::kChunkElems, 0, HeadCoord{0, 0},
                   bar_load);
     }
     if (mbar_wait(bar_load, 0, w, 1)) {

@@ -32,7 +32,7 @@
 extern "C" {
 #endif
 
-#define FA2_ABI_VERSION 1
+#define FA2_ABI_VERSION 2
 
 #define FA2_DTYPE_FP16 0
 #define FA2_DTYPE_BF16 1
@@ -49,6 +49,7 @@ extern "C" {
 #define FA2_ERR_SCALE (-9)             /* softmax scale not finite or not > 0 */
 #define FA2_ERR_WORKSPACE (-10)        /* dq_accum is NULL although deterministic == 0 */
 #define FA2_ERR_TOO_LARGE (-11)        /* fa2_bwd_static_scratch: B*H*ceil(N/128) > 4096 */
+#define FA2_ERR_STRIDE (-12)           /* a stride is <= 0, not a multiple of 8 elements, or row < D */
 
 /* Opaque stream handle: pass a cudaStream_t (NULL = legacy default stream). */
 typedef void* fa2_stream_t;
@@ -105,6 +106,35 @@ int fa2_bwd(const void* q, const void* k, const void* v, const void* dout,
 
 /* Bytes of fp32 workspace fa2_bwd needs (0 when deterministic != 0). */
 size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic);
+
+/*
+ * The same three operations on tensors that are not dense: any batch, head and row strides
+ * with a contiguous last dimension (for instance a [B, N, H, D] buffer viewed as
+ * [B, H, N, D]).  The reference makes such inputs contiguous with a copy
+ * (flash_attention_2.py:316, 170-171); here the strides go into the TMA descriptors and the
+ * copy disappears.
+ *
+ * `strides` holds one (batch, head, row) triple of ELEMENT strides per tensor argument, in
+ * argument order:
+ *     fa2_fwd_strided             q, k, v, o                      (12 values)
+ *     fa2_bwd_preprocess_strided  o, dout                         ( 6 values)
+ *     fa2_bwd_strided             q, k, v, dout, dq, dk, dv       (21 values)
+ * A triple of zeros means "dense"; strides == NULL means every tensor is dense (the plain
+ * entry points above are exactly that).  Every stride must be a positive multiple of 8
+ * elements (16 bytes) and the row stride at least D, else FA2_ERR_STRIDE; strides of
+ * dimensions of size 1 are ignored.  lse, rowstats and dq_accum keep their dense layouts.
+ */
+int fa2_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse,
+                    int B, int H, int N, int D, int dtype, float scale,
+                    const long long* strides, fa2_stream_t stream);
+int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse,
+                               float* rowstats, int B, int H, int N, int D, int dtype,
+                               const long long* strides, fa2_stream_t stream);
+int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dout,
+                    const float* rowstats,
+                    void* dq, void* dk, void* dv, float* dq_accum,
+                    int B, int H, int N, int D, int dtype, float scale, int deterministic,
+                    const long long* strides, fa2_stream_t stream);
 
 /*
  * Reads and clears the per-device status word that kernels set when a bounded wait

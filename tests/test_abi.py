@@ -38,7 +38,7 @@ def test_binding_table_covers_header():
 
 def test_abi_version_and_error_text():
     lib = _lib.lib()
-    assert lib.fa2_abi_version() == 1
+    assert lib.fa2_abi_version() == 2
     assert lib.fa2_strerror(0) == b"success"
     assert b"multiple of 8" in lib.fa2_strerror(-2)
     assert lib.fa2_strerror(-12345) == b"unknown fa2 error code"
@@ -97,3 +97,31 @@ def test_backward_argument_errors_need_no_gpu():
 def test_check_raises_with_text():
     with pytest.raises(_lib.Fa2Error, match="head dimension"):
         _lib.check("fa2_fwd", -2)
+
+
+@pytest.mark.parametrize(
+    "triple, code",
+    [
+        ((4, 64, 8192), -12),       # batch stride not a multiple of 8 elements
+        ((1 << 20, -64, 8192), -12),  # negative head stride
+        ((1 << 20, 64, 32), -12),   # row stride smaller than the head dim
+        ((1 << 20, 64, 0), -12),    # a zero stride inside a non-zero triple
+    ],
+)
+def test_stride_errors_need_no_gpu(triple, code):
+    """fa2_fwd_strided checks the (batch, head, row) element strides before touching the device."""
+    import ctypes
+
+    strides = (ctypes.c_longlong * 12)(*(list(triple) + [0] * 9))  # q strided, k, v, o dense
+    rc = _lib.lib().fa2_fwd_strided(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 2, 4, 128, 64, 0,
+                                    0.125, strides, None)
+    assert rc == code
+    assert b"stride" in _lib.lib().fa2_strerror(code)
+
+
+def test_stride_array_packs_batch_head_row_strides():
+    import torch
+
+    a = torch.empty(2, 5, 3, 16).transpose(1, 2)  # [B, H=3, N=5, D] view of [B, N, H, D] storage
+    arr = _lib.stride_array(a, a.contiguous())
+    assert list(arr) == [240, 16, 48, 240, 80, 16]

@@ -139,6 +139,58 @@ def test_non_contiguous_inputs_are_accepted():
     check_against(ref, got, torch.float16)
 
 
+def test_transposed_inputs_are_read_in_place():
+    """A [B, N, H, D] buffer viewed as [B, H, N, D] (what `x.view(B, N, H, D).transpose(1, 2)` of
+    a projection gives) goes to the kernels as it is; the reference copies it
+    (flash_attention_2.py:316)."""
+    from flash_attention_triton_b200.api import _as_kernel_input
+
+    q, k, v, do = make_inputs((2, 300, 3, 64), torch.bfloat16)  # [B, N, H, D] storage
+    qt, kt, vt, dot = (t.transpose(1, 2) for t in (q, k, v, do))
+    for t in (qt, kt, vt, dot):
+        on_device = t.to(DEV)  # keeps the strides
+        assert not on_device.is_contiguous() and _as_kernel_input(on_device) is on_device
+    ref = naive_attention(qt, kt, vt, dot)
+    for det in (True, False):
+        got = run_api(qt, kt, vt, dot, None, det)
+        check_against(ref, got, torch.bfloat16)
+        assert got["o"].is_contiguous()
+
+
+@pytest.mark.parametrize("det", [1, 0], ids=["det", "atomic"])
+def test_packed_qkv_through_the_strided_c_abi(det):
+    """q, k, v are slices of one [B, N, 3, H, D] buffer and dq, dk, dv are written straight into
+    the matching slices of a gradient buffer of the same layout: no copy on either side."""
+    b, h, n, d = 2, 3, 200, 96
+    g = torch.Generator().manual_seed(3)
+    qkv = torch.randn(b, n, 3, h, d, generator=g).to(torch.float16).to(DEV)
+    do = torch.randn(b, n, h, d, generator=g).to(torch.float16).to(DEV).transpose(1, 2)
+    q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+    dqkv = torch.full_like(qkv, float("nan"))
+    dq, dk, dv = (dqkv[:, :, i].transpose(1, 2) for i in range(3))
+    lib = _lib.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    scale = 1.0 / math.sqrt(d)
+    o = torch.empty(b, h, n, d, device=DEV, dtype=torch.float16)
+    lse = torch.empty(b, h, n, device=DEV, dtype=torch.float32)
+    assert lib.fa2_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
+                               lse.data_ptr(), b, h, n, d, 0, scale,
+                               _lib.stride_array(q, k, v, o), st) == 0
+    rs = torch.empty(lib.fa2_rowstats_bytes(b, h, n) // 4, device=DEV, dtype=torch.float32)
+    assert lib.fa2_bwd_preprocess_strided(o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                                          rs.data_ptr(), b, h, n, d, 0,
+                                          _lib.stride_array(o, do), st) == 0
+    ws = torch.empty(max(lib.fa2_bwd_workspace_bytes(b, h, n, d, det) // 4, 4), device=DEV)
+    assert lib.fa2_bwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(),
+                               rs.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                               ws.data_ptr(), b, h, n, d, 0, scale, det,
+                               _lib.stride_array(q, k, v, do, dq, dk, dv), st) == 0
+    assert _lib.device_status() == 0
+    ref = naive_attention(q.cpu(), k.cpu(), v.cpu(), do.cpu())
+    check_against(ref, {"o": o, "dq": dq, "dk": dk, "dv": dv}, torch.float16)
+    assert not torch.isnan(dqkv).any()  # every element of the packed gradient was written
+
+
 def test_unsupported_head_dim_and_seqlen_mismatch_raise():
     q = torch.randn(1, 1, 64, 160, device=DEV, dtype=torch.float16)
     with pytest.raises(ValueError, match="head dimension"):
