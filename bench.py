@@ -14,7 +14,8 @@ Printed JSON (one line, rank 0):
                recompute of the deterministic two-kernel backward is not counted).
   e2e          same metric through flash_attention_v2(...).backward() starting from pinned HOST
                tensors: host->device copies of q,k,v,dO and device->host copies of o,dq,dk,dv are
-               inside the timed region.
+               inside the timed region, every step; copy-in, compute and copy-out of
+               neighbouring steps overlap on three streams.
   roofline     tensor-core roofline of the dominant kernel (backward main), achieved = its
                algorithmic FLOPs / its own average launch duration (CUDA events around that
                launch), peak = MEASURED_PEAKS.json bf16_tflops (burst; kernel timed alone).
@@ -362,25 +363,50 @@ def main():
     # ------------------------------------------------------------ end to end (host buffers)
     e2e = None
     if not args.no_e2e:
+        # Every step copies its q, k, v, dO from pinned host memory, runs the public API and
+        # copies O, dq, dk, dv back.  The three stages run on three streams over two sets of
+        # device input buffers, so step i's copy-out, step i+1's compute and step i+2's copy-in
+        # overlap (PCIe is full duplex); all copies of all timed steps are inside the events.
         outs_host = [torch.empty(q.shape, dtype=dtype).pin_memory() for _ in range(4)]
+        main = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        dev_in = [[torch.empty(q.shape, dtype=dtype, device=dev) for _ in range(4)] for _ in range(2)]
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        in_free = [torch.cuda.Event() for _ in range(2)]
+        out_ready = torch.cuda.Event()
+        step_no = [0]
 
         def e2e_step():
-            qd, kd, vd, dod = (t.to(dev, non_blocking=True) for t in host)
-            qd.requires_grad_(True)
-            kd.requires_grad_(True)
-            vd.requires_grad_(True)
+            b = step_no[0] % 2
+            step_no[0] += 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(in_free[b])  # the step that last read this buffer set is done
+                for dst, src in zip(dev_in[b], host):
+                    dst.copy_(src, non_blocking=True)
+                in_ready[b].record(s_in)
+            main.wait_event(in_ready[b])
+            qd, kd, vd = (t.detach().requires_grad_(True) for t in dev_in[b][:3])
             out = flash_attention_v2(qd, kd, vd, scale_opt, bool(det))
-            out.backward(dod)
-            for dst, src in zip(outs_host, (out.detach(), qd.grad, kd.grad, vd.grad)):
-                dst.copy_(src, non_blocking=True)
+            out.backward(dev_in[b][3])
+            in_free[b].record(main)
+            out_ready.record(main)
+            results = (out.detach(), qd.grad, kd.grad, vd.grad)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(out_ready)
+                for dst, src in zip(outs_host, results):
+                    src.record_stream(s_out)
+                    dst.copy_(src, non_blocking=True)
 
-        for _ in range(2):
+        for _ in range(3):
             e2e_step()
+        torch.cuda.synchronize()
         e_steps = max(3, min(args.steps, 10))
         barrier()
         ev0.record()
         for _ in range(e_steps):
             e2e_step()
+        main.wait_stream(s_out)  # the last step's results have reached the host
+        main.wait_stream(s_in)
         ev1.record()
         torch.cuda.synchronize()
         barrier()
