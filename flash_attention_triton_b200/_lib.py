@@ -27,10 +27,10 @@ SYMBOLS = [
     ("fa2_device_status", c_int, [ctypes.POINTER(c_int)]),
     ("fa2_selftest_mma", c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     ("fa2_bwd_static_scratch", c_int, [c_void_p] * 9 + [c_int] * 5 + [c_float, c_void_p]),
-    ("fa2_fwd_strided", c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_void_p, c_void_p]),
+    ("fa2_fwd_strided", c_int, [c_void_p] * 5 + [c_int] * 6 + [c_float, c_void_p, c_void_p]),
     ("fa2_bwd_preprocess_strided", c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p, c_void_p]),
     ("fa2_bwd_strided", c_int,
-     [c_void_p] * 9 + [c_int] * 5 + [c_float, c_int, c_void_p, c_void_p]),
+     [c_void_p] * 9 + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p]),
 ]
 
 

@@ -14,7 +14,9 @@ Differences, all deliberate: fp16 and bf16 inputs run natively (the reference ca
 everything to fp16, lines 316/379); other float dtypes are cast to fp16 exactly as the
 reference does.  Head dimensions up to 128 are supported (multiples of 8 natively: the
 kernels run them zero-padded to 32 / 64 / 128 through TMA out-of-bounds fill; other sizes are
-zero-padded to a multiple of 8 on the host first) and ``seqlen_q == seqlen_k``.
+zero-padded to a multiple of 8 on the host first).  ``seqlen_q != seqlen_k`` follows the
+reference's top-left aligned causal mask: query row i sees keys ``0 .. min(i, seqlen_k - 1)``;
+keys beyond ``seqlen_q`` are seen by nobody and get zero gradients.
 Everything runs through the C library on the tensors' CUDA device; there is no fallback.
 """
 
@@ -80,8 +82,8 @@ def _flash_attention_forward(
     assert q.dtype == k.dtype == v.dtype, "All tensors must be the same type"
     if headdim > _MAX_HEAD_DIM or headdim % 8:
         raise ValueError(f"head dimension {headdim} is not supported (multiples of 8 up to {_MAX_HEAD_DIM})")
-    if seqlen_q != seqlen_k:
-        raise ValueError("seqlen_q must equal seqlen_k (causal self-attention)")
+    if seqlen_k > seqlen_q:  # no query sees the keys beyond seqlen_q - 1 (top-left aligned mask)
+        k, v, seqlen_k = k[:, :, :seqlen_q], v[:, :, :seqlen_q], seqlen_q
     softmax_scale = softmax_scale or 1.0 / math.sqrt(headdim)
     q, k, v = [_as_kernel_input(t) for t in (q, k, v)]
     output = torch.empty(q.shape, device=q.device, dtype=q.dtype)  # dense, like the reference's O
@@ -91,8 +93,8 @@ def _flash_attention_forward(
             "fa2_fwd_strided",
             _lib.lib().fa2_fwd_strided(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), output.data_ptr(), lse.data_ptr(),
-                batch, nheads, seqlen_q, headdim, _dtype_code(q.dtype), float(softmax_scale),
-                _lib.stride_array(q, k, v, output), _stream(q),
+                batch, nheads, seqlen_q, seqlen_k, headdim, _dtype_code(q.dtype),
+                float(softmax_scale), _lib.stride_array(q, k, v, output), _stream(q),
             ),
         )
     return output, lse, softmax_scale
@@ -118,12 +120,18 @@ def _flash_attention_backward(
     writes dQ once, already rounded.
     """
     batch, nheads, seqlen_q, headdim = q.shape
+    seqlen_k = k.shape[2]
+    if seqlen_k > seqlen_q:  # keys nobody sees: zero gradients, and the kernels skip them
+        dk[:, :, seqlen_q:].zero_()
+        dv[:, :, seqlen_q:].zero_()
+        k, v, dk, dv = (t[:, :, :seqlen_q] for t in (k, v, dk, dv))
+        seqlen_k = seqlen_q
     # The reference requires everything contiguous here (lines 183-192) and copies dO when it
     # is not (170-171); the inputs may keep their strides, only our own buffers are dense.
     q, k, v, d_output = [_as_kernel_input(t) for t in (q, k, v, d_output)]
     assert lse.shape == (batch, nheads, seqlen_q)
-    assert output.is_contiguous()
-    assert dq.is_contiguous() and dk.is_contiguous() and dv.is_contiguous()
+    assert output.is_contiguous() and dq.is_contiguous()
+    assert _readable_in_place(dk) and _readable_in_place(dv)
     lib = _lib.lib()
     code = _dtype_code(q.dtype)
     with torch.cuda.device(q.device):
@@ -147,8 +155,8 @@ def _flash_attention_backward(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), d_output.data_ptr(), rowstats.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                 dq_accum.data_ptr() if dq_accum is not None else None,
-                batch, nheads, seqlen_q, headdim, code, float(softmax_scale), int(deterministic),
-                _lib.stride_array(q, k, v, d_output, dq, dk, dv), _stream(q),
+                batch, nheads, seqlen_q, seqlen_k, headdim, code, float(softmax_scale),
+                int(deterministic), _lib.stride_array(q, k, v, d_output, dq, dk, dv), _stream(q),
             ),
         )
 

@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
                     const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                     const __grid_constant__ CUtensorMap tdk,
                     const __grid_constant__ CUtensorMap tdv, const float* __restrict__ rowstats,
-                    float* __restrict__ dq_accum, int N, float scale, float scale_log2,
+                    float* __restrict__ dq_accum, int N, int Nk, float scale, float scale_log2,
                     int* status) {
   using C = DkdvCfg<D, FUSE>;
   using T = Tile<D>;
@@ -176,7 +176,8 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
   const int jt = blockIdx.x;  // KV tile; tile 0 has the most Q tiles and is scheduled first
   const HeadCoord hc{static_cast<int>(blockIdx.y), static_cast<int>(blockIdx.z)};  // grid (tiles, H, B)
   const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
-  const int nq = ntiles - jt;  // Q tiles jt .. ntiles-1
+  const int nq = ntiles - jt;  // Q tiles jt .. ntiles-1 (N = query rows, Nk <= N = key rows)
+  const bool kv_ragged = jt * 128 + 128 > Nk;  // this KV tile has rows beyond the last key
   const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
   (void)traced;
 
@@ -415,11 +416,14 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
           p[2 * c4 + 1] = exp2_pair(t1, 2 * c4 + 1);
         }
       }
-      if (ii == 0) {  // diagonal tile: keep q >= kv
+      if (ii == 0 || kv_ragged) {
+        // diagonal tile: keep q >= kv; rows beyond the last key (zero-filled K, V) keep nothing,
+        // so that a huge 2^(-lse) never meets their zeros
+        const int first = (jt * 128 + r >= Nk) ? 128 : (ii == 0 ? r : 0);
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          p[c].x = (wg * 64 + 2 * c >= r) ? p[c].x : 0.f;
-          p[c].y = (wg * 64 + 2 * c + 1 >= r) ? p[c].y : 0.f;
+          p[c].x = (wg * 64 + 2 * c >= first) ? p[c].x : 0.f;
+          p[c].y = (wg * 64 + 2 * c + 1 >= first) ? p[c].y : 0.f;
         }
       }
       {
@@ -477,10 +481,10 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
       tc_fence_after();
       if (wg == 0)
         store_rows_16bit<D, BF16>(tmem_base + lane_base + C::kColDV, smem + C::kOffDO, w4, lane,
-                                  &tdv, jt * 128, hc, N);
+                                  &tdv, jt * 128, hc, Nk);
       else
         store_rows_16bit<D, BF16>(tmem_base + lane_base + C::kColDK, smem + C::kOffQ, w4, lane,
-                                  &tdk, jt * 128, hc, N);
+                                  &tdk, jt * 128, hc, Nk);
     }
   }
 
@@ -539,6 +543,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
     bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                   const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                   const __grid_constant__ CUtensorMap tdq, const float* __restrict__ rowstats, int N,
+                  int Nk,
                   float scale, float scale_log2, int* status) {
   using C = DqCfg<D>;
   using T = Tile<D>;
@@ -559,7 +564,8 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
   const int qt = ntiles - 1 - static_cast<int>(blockIdx.x);  // heaviest Q tile first
   const HeadCoord hc{static_cast<int>(blockIdx.y), static_cast<int>(blockIdx.z)};  // grid (tiles, H, B)
   const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
-  const int nkv = qt + 1;
+  const int nktiles = (Nk + 127) >> 7;               // N = query rows, Nk <= N = key rows
+  const int nkv = qt + 1 < nktiles ? qt + 1 : nktiles;  // KV tiles 0 .. min(qt, last)
   const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
   (void)traced;
 
@@ -751,11 +757,14 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
           p[c] = exp2_pair(t, c);
         }
       }
-      if (j == qt) {  // diagonal tile: keep kv <= q
+      if (j == qt || j * 128 + 128 > Nk) {
+        // diagonal tile: keep kv <= q; last KV tile: drop the columns beyond the last key
+        int last = j == qt ? r : 127;
+        last = last < Nk - 1 - j * 128 ? last : Nk - 1 - j * 128;
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          p[c].x = (wg * 64 + 2 * c <= r) ? p[c].x : 0.f;
-          p[c].y = (wg * 64 + 2 * c + 1 <= r) ? p[c].y : 0.f;
+          p[c].x = (wg * 64 + 2 * c <= last) ? p[c].x : 0.f;
+          p[c].y = (wg * 64 + 2 * c + 1 <= last) ? p[c].y : 0.f;
         }
       }
       FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 7);
@@ -810,11 +819,10 @@ cudaError_t launch_dkdv_t(const AttnShape& s, const CUtensorMap& tq, const CUten
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
-  const int ntiles = (s.N + 127) / 128;
-  dim3 grid(ntiles, s.H, s.B);
+  dim3 grid((s.Nk + 127) / 128, s.H, s.B);  // one CTA per KV tile
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum,
-                                                     s.N, s.scale, s.scale * 1.4426950408889634f,
-                                                     status);
+                                                     s.N, s.Nk, s.scale,
+                                                     s.scale * 1.4426950408889634f, status);
   return cudaGetLastError();
 }
 
@@ -829,8 +837,9 @@ cudaError_t launch_dq_t(const AttnShape& s, const CUtensorMap& tq, const CUtenso
   if (e != cudaSuccess) return e;
   const int ntiles = (s.N + 127) / 128;
   dim3 grid(ntiles, s.H, s.B);
-  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, rowstats, s.N, s.scale,
-                                                     s.scale * 1.4426950408889634f, status);
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdq, rowstats, s.N, s.Nk,
+                                                     s.scale, s.scale * 1.4426950408889634f,
+                                                     status);
   return cudaGetLastError();
 }
 

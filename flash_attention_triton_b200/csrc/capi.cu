@@ -147,8 +147,8 @@ int check_shape(int B, int H, int N, int D, int dtype) {
   return FA2_OK;
 }
 
-AttnShape make_shape(int B, int H, int N, int D, int dtype, float scale) {
-  return AttnShape{B, H, N, padded_head_dim(D), dtype, scale, D};
+AttnShape make_shape(int B, int H, int N, int Nk, int D, int dtype, float scale) {
+  return AttnShape{B, H, N, padded_head_dim(D), dtype, scale, D, Nk};
 }
 
 }  // namespace
@@ -167,7 +167,7 @@ const char* fa2_strerror(int code) {
     case FA2_ERR_HEAD_DIM: return "head dimension must be a multiple of 8 between 8 and 128";
     case FA2_ERR_DTYPE: return "dtype must be 0 (fp16) or 1 (bf16)";
     case FA2_ERR_MISALIGNED: return "tensor pointers must be 16-byte aligned";
-    case FA2_ERR_SHAPE: return "B, H, N must be positive, B*H <= 65535, N <= 2^24";
+    case FA2_ERR_SHAPE: return "B, H, N must be positive, B*H <= 65535, N <= 2^24, 1 <= Nk <= N";
     case FA2_ERR_ARCH: return "the current device is not compute capability 10.x (B200)";
     case FA2_ERR_DEVICE_STATUS: return "a kernel abandoned a bounded wait (see fa2_device_status)";
     case FA2_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
@@ -183,24 +183,25 @@ const char* fa2_strerror(int code) {
 }
 
 int fa2_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
-                    int N, int D, int dtype, float scale, const long long* strides,
+                    int N, int Nk, int D, int dtype, float scale, const long long* strides,
                     fa2_stream_t stream) {
   if (!q || !k || !v || !o || !lse) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
+  if (Nk < 1 || Nk > N) return FA2_ERR_SHAPE;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o)) return FA2_ERR_MISALIGNED;
   if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
   for (int idx = 0; idx < 4; ++idx) {
     Strides unused;
-    if (int e = get_strides(strides, idx, B, H, N, D, &unused)) return e;
+    if (int e = get_strides(strides, idx, B, H, idx == 1 || idx == 2 ? Nk : N, D, &unused)) return e;
   }
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
   CUtensorMap tq, tk, tv, to;
   if (int e = make_map_of(&tq, q, strides, 0, dtype, B, H, N, D, 128)) return e;
-  if (int e = make_map_of(&tk, k, strides, 1, dtype, B, H, N, D, 128)) return e;
-  if (int e = make_map_of(&tv, v, strides, 2, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&tk, k, strides, 1, dtype, B, H, Nk, D, 128)) return e;
+  if (int e = make_map_of(&tv, v, strides, 2, dtype, B, H, Nk, D, 128)) return e;
   if (int e = make_map_of(&to, o, strides, 3, dtype, B, H, N, D, 32)) return e;
-  const AttnShape s = make_shape(B, H, N, D, dtype, scale);
+  const AttnShape s = make_shape(B, H, N, Nk, D, dtype, scale);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   LaunchCtx ctx;
   make_ctx(d, &ctx);
@@ -209,7 +210,7 @@ int fa2_fwd_strided(const void* q, const void* k, const void* v, void* o, float*
 
 int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H, int N,
             int D, int dtype, float scale, fa2_stream_t stream) {
-  return fa2_fwd_strided(q, k, v, o, lse, B, H, N, D, dtype, scale, nullptr, stream);
+  return fa2_fwd_strided(q, k, v, o, lse, B, H, N, N, D, dtype, scale, nullptr, stream);
 }
 
 size_t fa2_rowstats_bytes(int B, int H, int N) {
@@ -229,7 +230,7 @@ int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse
   if (int e = get_strides(strides, 1, B, H, N, D, &sdo)) return e;
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
-  const AttnShape s = make_shape(B, H, N, D, dtype, 1.f);
+  const AttnShape s = make_shape(B, H, N, N, D, dtype, 1.f);
   return static_cast<int>(launch_bwd_preprocess(s, o, so, dout, sdo, lse, rowstats,
                                                 static_cast<cudaStream_t>(stream)));
 }
@@ -247,33 +248,35 @@ size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
 
 int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dout,
                     const float* rowstats, void* dq, void* dk, void* dv, float* dq_accum, int B,
-                    int H, int N, int D, int dtype, float scale, int deterministic,
+                    int H, int N, int Nk, int D, int dtype, float scale, int deterministic,
                     const long long* strides, fa2_stream_t stream) {
   if (!q || !k || !v || !dout || !rowstats || !dq || !dk || !dv) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
+  if (Nk < 1 || Nk > N) return FA2_ERR_SHAPE;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(dout) || !aligned16(dq) ||
       !aligned16(dk) || !aligned16(dv) || !aligned16(rowstats))
     return FA2_ERR_MISALIGNED;
   if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
   if (!deterministic && !dq_accum) return FA2_ERR_WORKSPACE;
   if (!deterministic && !aligned16(dq_accum)) return FA2_ERR_MISALIGNED;
+  const int rows_of[7] = {N, Nk, Nk, N, N, Nk, Nk};  // q, k, v, dout, dq, dk, dv
   for (int idx = 0; idx < 7; ++idx) {
     Strides unused;
-    if (int e = get_strides(strides, idx, B, H, N, D, &unused)) return e;
+    if (int e = get_strides(strides, idx, B, H, rows_of[idx], D, &unused)) return e;
   }
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   if (int e = make_map_of(&tq, q, strides, 0, dtype, B, H, N, D, 128)) return e;
-  if (int e = make_map_of(&tk, k, strides, 1, dtype, B, H, N, D, 128)) return e;
-  if (int e = make_map_of(&tv, v, strides, 2, dtype, B, H, N, D, 128)) return e;
+  if (int e = make_map_of(&tk, k, strides, 1, dtype, B, H, Nk, D, 128)) return e;
+  if (int e = make_map_of(&tv, v, strides, 2, dtype, B, H, Nk, D, 128)) return e;
   if (int e = make_map_of(&tdo, dout, strides, 3, dtype, B, H, N, D, 128)) return e;
-  if (int e = make_map_of(&tdk, dk, strides, 5, dtype, B, H, N, D, 32)) return e;
-  if (int e = make_map_of(&tdv, dv, strides, 6, dtype, B, H, N, D, 32)) return e;
+  if (int e = make_map_of(&tdk, dk, strides, 5, dtype, B, H, Nk, D, 32)) return e;
+  if (int e = make_map_of(&tdv, dv, strides, 6, dtype, B, H, Nk, D, 32)) return e;
   Strides sdq;
   if (int e = get_strides(strides, 4, B, H, N, D, &sdq)) return e;
-  const AttnShape s = make_shape(B, H, N, D, dtype, scale);
+  const AttnShape s = make_shape(B, H, N, Nk, D, dtype, scale);
   if (deterministic) {
     if (int e = make_map(&tdq, dq, dtype, B, H, N, D, sdq, 32)) return e;
     cudaError_t ce =
@@ -291,8 +294,8 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
 int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const float* rowstats,
             void* dq, void* dk, void* dv, float* dq_accum, int B, int H, int N, int D, int dtype,
             float scale, int deterministic, fa2_stream_t stream) {
-  return fa2_bwd_strided(q, k, v, dout, rowstats, dq, dk, dv, dq_accum, B, H, N, D, dtype, scale,
-                         deterministic, nullptr, stream);
+  return fa2_bwd_strided(q, k, v, dout, rowstats, dq, dk, dv, dq_accum, B, H, N, N, D, dtype,
+                         scale, deterministic, nullptr, stream);
 }
 
 int fa2_device_status(int* status_out) {

@@ -46,12 +46,15 @@ __host__ __device__ __forceinline__ uint32_t swizzled_offset_128B(uint32_t row, 
 // Tensor maps describe [B, H, N, D] tensors with box (CH, 128 or 32, 1, 1).
 // ----------------------------------------------------------------------------------------
 struct AttnShape {
-  int B, H, N;
+  int B, H;
+  int N;      // query rows (rows of q, o, dout, dq, lse)
   int D;      // head dim the kernels are instantiated for: 32, 64 or 128
   int dtype;  // 0 = fp16, 1 = bf16
   float scale;
   int Dg;     // head dim of the tensors in memory (a multiple of 8, <= D); the columns
               // Dg..D-1 are zeros on TMA loads and dropped on TMA stores
+  int Nk;     // key rows (rows of k, v, dk, dv), 1 <= Nk <= N; the causal mask is aligned at
+              // the top left: query row i sees keys 0 .. min(i, Nk - 1)
 };
 
 // Element strides of one [B, H, N, D] tensor (the last dimension is contiguous).

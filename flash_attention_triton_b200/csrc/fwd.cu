@@ -85,8 +85,8 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
     fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap to,
-               float* __restrict__ lse, int N, int num_bh, int num_heads, float scale_log2,
-               int* status, unsigned int* work_counter) {
+               float* __restrict__ lse, int N, int Nk, int num_bh, int num_heads,
+               float scale_log2, int* status, unsigned int* work_counter) {
   using C = FwdCfg<D>;
   using T = Tile<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
@@ -109,6 +109,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
   auto bar = [&](int i) { return smem_base + C::kOffBar + 8u * i; };
 
   const int ntiles = (N + 127) >> 7;
+  const int nktiles = (Nk + 127) >> 7;
   const int npairs = (ntiles + 1) >> 1;
   const int total_items = npairs * num_bh;
 
@@ -164,9 +165,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const int pair = npairs - 1 - (item - bh * npairs);  // heavy pairs of a head first
     const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
     const bool has1 = qt1 < ntiles;
-    const int n0 = qt0 + 1;             // KV tiles of Q tile 0
-    const int n1 = has1 ? qt1 + 1 : 0;  // KV tiles of Q tile 1 (one more than tile 0)
-    const int nkv = has1 ? n1 : n0;
+    // KV tiles of Q tile i: 0 .. min(i, last KV tile)  (N = query rows, Nk <= N = key rows)
+    const int n0 = qt0 + 1 < nktiles ? qt0 + 1 : nktiles;
+    const int n1 = has1 ? (qt1 + 1 < nktiles ? qt1 + 1 : nktiles) : 0;
+    const int nkv = n1 > n0 ? n1 : n0;
     const bool traced = item == 0;  // used by FA2_TRACE_EVENT only
     (void)traced;
 
@@ -306,9 +308,12 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, j * 16 + 9);
       FA2_TRACE_EVENT(traced && lane == 0, 8192 + j * 16 + 8 + warp);
       float* s = reinterpret_cast<float*>(sr);
-      if (j == qt) {  // diagonal tile: keep col <= row
+      if (j == qt || j * 128 + 128 > Nk) {
+        // diagonal tile: keep col <= row; last KV tile: drop the columns beyond the last key
+        int last = j == qt ? r : 127;
+        last = last < Nk - 1 - j * 128 ? last : Nk - 1 - j * 128;
 #pragma unroll
-        for (int c = 0; c < 128; ++c) s[c] = (c <= r) ? s[c] : -INFINITY;
+        for (int c = 0; c < 128; ++c) s[c] = (c <= last) ? s[c] : -INFINITY;
       }
       float mx[4];
 #pragma unroll
@@ -445,7 +450,7 @@ cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtens
   const long long items = static_cast<long long>(npairs) * s.B * s.H;
   const unsigned grid = static_cast<unsigned>(items < ctx.num_sms ? items : ctx.num_sms);
   const float scale_log2 = s.scale * 1.4426950408889634f;
-  kern<<<grid, kFwdThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, lse, s.N, s.B * s.H, s.H,
+  kern<<<grid, kFwdThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, lse, s.N, s.Nk, s.B * s.H, s.H,
                                                      scale_log2, ctx.status, ctx.work_counter);
   return cudaGetLastError();
 }

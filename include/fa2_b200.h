@@ -42,7 +42,7 @@ extern "C" {
 #define FA2_ERR_HEAD_DIM (-2)          /* D not a multiple of 8 in [8, 128] */
 #define FA2_ERR_DTYPE (-3)             /* dtype not FA2_DTYPE_FP16 / FA2_DTYPE_BF16 */
 #define FA2_ERR_MISALIGNED (-4)        /* a tensor pointer is not 16-byte aligned */
-#define FA2_ERR_SHAPE (-5)             /* B, H or N <= 0, or B*H > 65535, or N too large */
+#define FA2_ERR_SHAPE (-5)             /* B, H or N <= 0, B*H > 65535, N too large, Nk not in [1, N] */
 #define FA2_ERR_ARCH (-6)              /* current device is not compute capability 10.x */
 #define FA2_ERR_DEVICE_STATUS (-7)     /* a kernel gave up on a bounded wait */
 #define FA2_ERR_DRIVER (-8)            /* cuTensorMapEncodeTiled unavailable or failed */
@@ -123,9 +123,15 @@ size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic);
  * entry points above are exactly that).  Every stride must be a positive multiple of 8
  * elements (16 bytes) and the row stride at least D, else FA2_ERR_STRIDE; strides of
  * dimensions of size 1 are ignored.  lse, rowstats and dq_accum keep their dense layouts.
+ *
+ * They also take the number of key rows separately: q, o, dout, dq and lse have N rows, k, v,
+ * dk and dv have Nk rows, 1 <= Nk <= N.  The causal mask is aligned at the top left like the
+ * reference's (_triton_kernels_v2.py:139-147): query row i sees keys 0 .. min(i, Nk - 1).
+ * Keys beyond row N - 1 would never be seen by any query, which is why Nk > N is refused
+ * (FA2_ERR_SHAPE): pass the first N rows of k and v and zero the rest of dk and dv.
  */
 int fa2_fwd_strided(const void* q, const void* k, const void* v, void* o, float* lse,
-                    int B, int H, int N, int D, int dtype, float scale,
+                    int B, int H, int N, int Nk, int D, int dtype, float scale,
                     const long long* strides, fa2_stream_t stream);
 int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse,
                                float* rowstats, int B, int H, int N, int D, int dtype,
@@ -133,8 +139,8 @@ int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse
 int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dout,
                     const float* rowstats,
                     void* dq, void* dk, void* dv, float* dq_accum,
-                    int B, int H, int N, int D, int dtype, float scale, int deterministic,
-                    const long long* strides, fa2_stream_t stream);
+                    int B, int H, int N, int Nk, int D, int dtype, float scale,
+                    int deterministic, const long long* strides, fa2_stream_t stream);
 
 /*
  * Reads and clears the per-device status word that kernels set when a bounded wait

@@ -43,7 +43,9 @@ def naive_attention(
     """Causal attention by its definition, with analytic gradients.
 
     Inputs ``[B, H, N, D]`` (any float dtype; they are up-cast to ``dtype`` as they are, so
-    pass tensors already rounded to the kernel's 16-bit dtype to isolate kernel error).
+    pass tensors already rounded to the kernel's 16-bit dtype to isolate kernel error).  ``k``
+    and ``v`` may have a different number of rows than ``q``; the mask ``row >= col`` is then
+    aligned at the top left, as in the reference's kernels (``_triton_kernels_v2.py:139-147``).
     Returns ``o, lse`` and, when ``dout`` is given, ``dq, dk, dv, delta``.
     Formula: ``tests/test_flash_attention_2.py:289-294`` of the reference; backward is the
     chain rule the reference's kernel implements (``_triton_kernels_v2.py:312-343``).
@@ -51,7 +53,7 @@ def naive_attention(
     qf, kf, vf = (t.detach().to("cpu", dtype) for t in (q, k, v))
     n, d = qf.shape[-2], qf.shape[-1]
     scale = softmax_scale or 1.0 / math.sqrt(d)
-    mask = torch.ones(n, n, dtype=torch.bool).tril()
+    mask = torch.ones(n, kf.shape[-2], dtype=torch.bool).tril()
     s = (qf @ kf.transpose(-1, -2)) * scale
     s = s.masked_fill(~mask, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
@@ -110,6 +112,7 @@ def reference_tiled(
     """
     q, k, v, dout = (np.asarray(t, dtype=np.float16).astype(np.float32) for t in (q, k, v, dout))
     b, h, n, d = q.shape
+    nk = k.shape[2]  # key rows; the causal mask is aligned at the top left (:139-147)
     s32 = np.float32(softmax_scale)
     o = np.zeros((b, h, n, d), np.float32)
     lse_out = np.zeros((b, h, n), np.float32)
@@ -124,9 +127,9 @@ def reference_tiled(
                     lse = np.full(len(rows), neg_inf, np.float32)
                     m = np.full(len(rows), neg_inf, np.float32)
                     acc = np.zeros((len(rows), d), np.float32)
-                    end = min(q0 + block_q, n)
+                    end = min(q0 + block_q, nk)  # (:76)
                     for k0 in range(0, end, block_kv):
-                        cols = np.arange(k0, min(k0 + block_kv, n))
+                        cols = np.arange(k0, min(k0 + block_kv, nk))
                         sc = qb @ k[bi, hi, cols].T  # fp32 accumulate (:137-138)
                         sc = np.where(rows[:, None] >= cols[None, :], sc, neg_inf)  # (:142-147)
                         m_new = np.maximum((sc * s32).max(axis=1), lse)  # (:150) max with lse
@@ -143,12 +146,12 @@ def reference_tiled(
         delta = (o * dout).sum(axis=-1, dtype=np.float32)
         # ---------------------------------------------------------------- backward, :312-343
         dq_acc = np.zeros((b, h, n, d), np.float32)
-        dk = np.zeros((b, h, n, d), np.float32)
-        dv = np.zeros((b, h, n, d), np.float32)
+        dk = np.zeros((b, h, nk, d), np.float32)
+        dv = np.zeros((b, h, nk, d), np.float32)
         for bi in range(b):
             for hi in range(h):
-                for k0 in range(0, n, bwd_block):
-                    cols = np.arange(k0, min(k0 + bwd_block, n))
+                for k0 in range(0, nk, bwd_block):
+                    cols = np.arange(k0, min(k0 + bwd_block, nk))
                     kb, vb = k[bi, hi, cols], v[bi, hi, cols]
                     dk_acc = np.zeros((len(cols), d), np.float32)
                     dv_acc = np.zeros((len(cols), d), np.float32)

@@ -22,18 +22,22 @@ os.environ["TRITON_INTERPRET"] = "1"  # must precede the triton import
 
 HERE = Path(__file__).resolve().parent
 
-# name, (B, H, N, D), softmax_scale (None = default), q/k multiplier, fwd tile, bwd tile, seq-parallel
+# name, (B, H, N, D), softmax_scale (None = default), q/k multiplier, fwd tile, bwd tile,
+# seq-parallel, key rows (None = N; otherwise k and v have that many rows)
 CASES = [
-    ("c1_fp16_2x4x256x64_det", (2, 4, 256, 64), None, 1.0, 64, 64, False),
-    ("ragged_fp16_1x2x191x32_det", (1, 2, 191, 32), 0.5, 3.0, 64, 64, False),
-    ("ragged_fp16_1x2x191x32_seqpar", (1, 2, 191, 32), 0.5, 3.0, 64, 64, True),
-    ("d128_fp16_1x2x160x128_det", (1, 2, 160, 128), None, 1.0, 32, 32, False),
+    ("c1_fp16_2x4x256x64_det", (2, 4, 256, 64), None, 1.0, 64, 64, False, None),
+    ("ragged_fp16_1x2x191x32_det", (1, 2, 191, 32), 0.5, 3.0, 64, 64, False, None),
+    ("ragged_fp16_1x2x191x32_seqpar", (1, 2, 191, 32), 0.5, 3.0, 64, 64, True, None),
+    ("d128_fp16_1x2x160x128_det", (1, 2, 160, 128), None, 1.0, 32, 32, False, None),
+    ("fewer_keys_fp16_1x2_q200_k70_d32_det", (1, 2, 200, 32), None, 1.0, 64, 64, False, 70),
+    ("more_keys_fp16_1x2_q100_k170_d64_det", (1, 2, 100, 64), None, 1.0, 64, 64, False, 170),
 ]
 
 
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default="/root/reference/src")
+    ap.add_argument("--only", default="", help="substring of the case names to (re)generate")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
 
@@ -48,9 +52,12 @@ def main() -> None:
     from flash_attention_triton import KernelsConfigV2, init_to_zero_v2
     from flash_attention_triton._triton_kernels_v2 import _forward_kernel
 
-    for name, (b, h, n, d), scale, qk_mul, fwd_blk, bwd_blk, seqpar in CASES:
+    for name, (b, h, n, d), scale, qk_mul, fwd_blk, bwd_blk, seqpar, nk in CASES:
+        if args.only not in name:
+            continue
+        nk = nk or n
         g = torch.Generator(device="cpu").manual_seed(0)
-        q, k, v, do = (torch.randn(b, h, n, d, generator=g) for _ in range(4))
+        q, k, v, do = (torch.randn(b, h, rows, d, generator=g) for rows in (n, nk, nk, n))
         q, k = q * qk_mul, k * qk_mul
         q, k, v, do = (t.half() for t in (q, k, v, do))
         sc = scale or 1.0 / math.sqrt(d)
@@ -71,10 +78,10 @@ def main() -> None:
             q, k, v, out, lse, spd, sc,
             q.stride(0), q.stride(1), q.stride(2), k.stride(0), k.stride(1), k.stride(2),
             v.stride(0), v.stride(1), v.stride(2), out.stride(0), out.stride(1), out.stride(2),
-            h, n, n, nr, d, n // 32, n // 32, bhd,
+            h, n, nk, nr, d, n // 32, nk // 32, bhd,
             BLOCK_Q_ROWS_SIZE=fwd_blk, BLOCK_KV_COLS_SIZE=fwd_blk,
         )
-        dq, dk, dv = (torch.empty_like(q) for _ in range(3))
+        dq, dk, dv = (torch.empty_like(t) for t in (q, k, v))
         fa._flash_attention_backward(q, k, v, out, lse, dq, dk, dv, do, sc, cfg)
         np.savez_compressed(
             HERE / f"{name}.npz",

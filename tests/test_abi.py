@@ -113,7 +113,7 @@ def test_stride_errors_need_no_gpu(triple, code):
     import ctypes
 
     strides = (ctypes.c_longlong * 12)(*(list(triple) + [0] * 9))  # q strided, k, v, o dense
-    rc = _lib.lib().fa2_fwd_strided(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 2, 4, 128, 64, 0,
+    rc = _lib.lib().fa2_fwd_strided(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 2, 4, 128, 128, 64, 0,
                                     0.125, strides, None)
     assert rc == code
     assert b"stride" in _lib.lib().fa2_strerror(code)
@@ -125,3 +125,13 @@ def test_stride_array_packs_batch_head_row_strides():
     a = torch.empty(2, 5, 3, 16).transpose(1, 2)  # [B, H=3, N=5, D] view of [B, N, H, D] storage
     arr = _lib.stride_array(a, a.contiguous())
     assert list(arr) == [240, 16, 48, 240, 80, 16]
+
+
+def test_key_count_must_not_exceed_query_count():
+    """Keys beyond the last query row are never attended under the top-left aligned mask; the C
+    entry points refuse them (the Python API slices them off and zeroes their gradients)."""
+    lib = _lib.lib()
+    assert lib.fa2_fwd_strided(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 1, 1, 128, 129, 64, 0,
+                               0.125, None, None) == -5
+    assert lib.fa2_fwd_strided(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 1, 1, 128, 0, 64, 0,
+                               0.125, None, None) == -5

@@ -174,7 +174,7 @@ def test_packed_qkv_through_the_strided_c_abi(det):
     o = torch.empty(b, h, n, d, device=DEV, dtype=torch.float16)
     lse = torch.empty(b, h, n, device=DEV, dtype=torch.float32)
     assert lib.fa2_fwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                               lse.data_ptr(), b, h, n, d, 0, scale,
+                               lse.data_ptr(), b, h, n, n, d, 0, scale,
                                _lib.stride_array(q, k, v, o), st) == 0
     rs = torch.empty(lib.fa2_rowstats_bytes(b, h, n) // 4, device=DEV, dtype=torch.float32)
     assert lib.fa2_bwd_preprocess_strided(o.data_ptr(), do.data_ptr(), lse.data_ptr(),
@@ -183,7 +183,7 @@ def test_packed_qkv_through_the_strided_c_abi(det):
     ws = torch.empty(max(lib.fa2_bwd_workspace_bytes(b, h, n, d, det) // 4, 4), device=DEV)
     assert lib.fa2_bwd_strided(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(),
                                rs.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                               ws.data_ptr(), b, h, n, d, 0, scale, det,
+                               ws.data_ptr(), b, h, n, n, d, 0, scale, det,
                                _lib.stride_array(q, k, v, do, dq, dk, dv), st) == 0
     assert _lib.device_status() == 0
     ref = naive_attention(q.cpu(), k.cpu(), v.cpu(), do.cpu())
@@ -191,14 +191,32 @@ def test_packed_qkv_through_the_strided_c_abi(det):
     assert not torch.isnan(dqkv).any()  # every element of the packed gradient was written
 
 
-def test_unsupported_head_dim_and_seqlen_mismatch_raise():
+def test_unsupported_head_dim_raises():
     q = torch.randn(1, 1, 64, 160, device=DEV, dtype=torch.float16)
     with pytest.raises(ValueError, match="head dimension"):
         flash_attention_v2(q, q, q)
-    q = torch.randn(1, 1, 64, 64, device=DEV, dtype=torch.float16)
-    k = torch.randn(1, 1, 32, 64, device=DEV, dtype=torch.float16)
-    with pytest.raises(ValueError, match="seqlen"):
-        flash_attention_v2(q, k, k)
+
+
+@pytest.mark.parametrize("det", [True, False], ids=["det", "atomic"])
+@pytest.mark.parametrize(
+    "nq,nk,d,dtype",
+    [
+        (300, 100, 64, torch.float16),    # keys end inside the first tile: every later row sees all
+        (1000, 257, 128, torch.bfloat16),  # ragged last KV tile seen by many Q tiles
+        (640, 384, 32, torch.float16),    # tile-aligned key count
+        (200, 520, 64, torch.bfloat16),   # more keys than queries: the tail gets zero gradients
+        (129, 1, 64, torch.float16),      # a single key
+    ],
+)
+def test_seqlen_q_differs_from_seqlen_k(nq, nk, d, dtype, det):
+    """Top-left aligned causal mask as in the reference (_triton_kernels_v2.py:139-147):
+    query row i sees keys 0 .. min(i, seqlen_k - 1)."""
+    g = torch.Generator().manual_seed(nq + nk)
+    q, do = (torch.randn(2, 2, nq, d, generator=g).to(dtype) for _ in range(2))
+    k, v = (torch.randn(2, 2, nk, d, generator=g).to(dtype) for _ in range(2))
+    ref = naive_attention(q, k, v, do)
+    got = run_api(q, k, v, do, None, det)
+    check_against(ref, got, dtype)
 
 
 # --------------------------------------------------------------------------- golden vectors

@@ -14,21 +14,23 @@ GOLDEN = sorted(GOLDEN_DIR.glob("*.npz"))
 
 
 def test_golden_files_present():
-    assert len(GOLDEN) >= 4
+    assert len(GOLDEN) >= 6
 
 
 @pytest.mark.parametrize("path", GOLDEN, ids=lambda p: p.stem)
 def test_restatement_matches_reference_kernels(path):
-    """The numpy restatement reproduces the reference kernels: bit-exact for three of the four
-    cases; in the d=128 case BLAS blocking reorders a 128-long fp32 sum, which can move a
-    result across an fp16 rounding boundary, so the bound is one fp16 ulp (2^-10 relative,
-    5e-4 absolute near zero)."""
+    """The numpy restatement reproduces the reference kernels: bit-exact for four of the six
+    cases (square and more-keys-than-queries).  In the d=128 case BLAS blocking reorders a
+    128-long fp32 sum, and in the fewer-keys case ten lse values differ in the last fp32 bit
+    (numpy's exp/log against the interpreter's); either can move a result across an fp16
+    rounding boundary, so the bound there is one fp16 ulp (2^-10 relative, 5e-4 absolute near
+    zero)."""
     z = np.load(path)
     r = reference_tiled(
         z["q"], z["k"], z["v"], z["dout"], float(z["softmax_scale"]),
         int(z["fwd_block"]), int(z["fwd_block"]), int(z["bwd_block"]),
     )
-    exact = "d128" not in path.stem
+    exact = "d128" not in path.stem and "fewer_keys" not in path.stem
     for key in ("o", "dq", "dk", "dv"):
         if exact:
             assert np.array_equal(r[key], z[key]), key
