@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
   const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
   const int nq = ntiles - jt;  // Q tiles jt .. ntiles-1 (N = query rows, Nk <= N = key rows)
   const bool kv_ragged = jt * 128 + 128 > Nk;  // this KV tile has rows beyond the last key
-  const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
+  const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;  // FA2_TRACE_EVENT only
   (void)traced;
 
   if (threadIdx.x == 0) {
@@ -528,8 +528,8 @@ struct DqCfg {
   static constexpr int kBarDpFull = kBarSFull + 2;
   static constexpr int kBarDpConsumed = kBarDpFull + 1;  // 8 arrivals (one per compute warp)
   static constexpr int kBarDsReady = kBarDpConsumed + 1;  // 8 arrivals
-  static constexpr int kBarDqDone = kBarDsReady + 1;      // dQ += dS(j) K_j completed
-  static constexpr int kBarDone = kBarDqDone + 1;
+  static constexpr int kBarDqDone = kBarDsReady + 1;      // 2: dQ += dS(j) K_j completed, by j%2
+  static constexpr int kBarDone = kBarDqDone + 2;
   static constexpr int kNumBars = kBarDone + 1;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
   static constexpr int kColS = 0;     // score buffers at 0 and 128; dS (16-bit) overwrites them
@@ -566,7 +566,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
   const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
   const int nktiles = (Nk + 127) >> 7;               // N = query rows, Nk <= N = key rows
   const int nkv = qt + 1 < nktiles ? qt + 1 : nktiles;  // KV tiles 0 .. min(qt, last)
-  const bool traced = blockIdx.x == 0 && blockIdx.y == 0;  // used by FA2_TRACE_EVENT only
+  const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;  // FA2_TRACE_EVENT only
   (void)traced;
 
   if (threadIdx.x == 0) {
@@ -584,7 +584,8 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
     mbar_init(bar(C::kBarDpFull), 1);
     mbar_init(bar(C::kBarDpConsumed), 8);
     mbar_init(bar(C::kBarDsReady), 8);
-    mbar_init(bar(C::kBarDqDone), 1);
+    mbar_init(bar(C::kBarDqDone + 0), 1);
+    mbar_init(bar(C::kBarDqDone + 1), 1);
     mbar_init(bar(C::kBarDone), 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -641,59 +642,62 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
         }
       }
     } else if (warp == C::kMmaWarp) {
-      // ------------------------------------------------------------ warp X: S and dP products
-      // (whole warp converged, the elected lane issues).  dQ products are issued by warp
-      // kMmaWarp + 2 so that neither stream waits behind the other's barriers; the one
-      // hazard between the streams, S(j+2) overwriting dS(j) while dQ(j) still reads it, is
-      // covered by the dq_done barrier.
+      // ------------------------------------------------------------ warp X: dP(j) = dO V_j^T
+      // (whole warp converged, the elected lane issues).  The three products of a KV step are
+      // issued by three warps (X: dP, Z: S, Y: dQ), so none of them waits behind another
+      // one's barrier: dP(j+1) only needs the compute warps to have read dP(j), S(j+2) only
+      // needs dQ(j) to have consumed dS(j) (both live in score buffer j%2), dQ(j) only needs
+      // dS(j).  The tensor pipe executes whatever is issued first.
       const uint32_t elected = elect_one();
       auto commit = [&](int b) {
         if (elected) mma_commit(bar(b));
       };
-      const uint32_t qa = smem_base + C::kOffQ, doa = smem_base + C::kOffDO;
-      int ks = 0, kph = 0, vs = 0, vph = 0;  // ring positions of the next K / V tile to use
-      auto issue_s = [&](int j) -> bool {   // S(j) -> score buffer j%2, K ring position (ks, kph)
-        if (!mbar_wait(bar(C::kBarKFull + ks), kph, w, kBSiteMmaKV)) return false;
-        issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS + (j & 1) * 128, qa,
-                                   smem_base + C::kOffK + ks * T::kTileBytes);
-        commit(C::kBarSFull + (j & 1));
-        commit(C::kBarKEmpty + ks);
-        if (++ks == C::kKStages) {
-          ks = 0;
-          kph ^= 1;
+      const uint32_t doa = smem_base + C::kOffDO;
+      int vs = 0, vph = 0;  // ring position of the next V tile
+      bool ok = mbar_wait(bar(C::kBarQ), 0, w, kBSiteMmaQ);
+      for (int j = 0; ok && j < nkv; ++j) {
+        if (j > 0) {
+          // dP columns are free once every compute warp has read dP(j-1)
+          if (!(ok = mbar_wait(bar(C::kBarDpConsumed), (j - 1) & 1, w, kBSiteMmaDrain))) break;
+          tc_fence_after();
         }
-        return true;
-      };
-      auto issue_dp = [&]() -> bool {  // dP of the next V tile; V is free afterwards
-        if (!mbar_wait(bar(C::kBarVFull + vs), vph, w, kBSiteMmaDO)) return false;
+        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 0);
+        if (!(ok = mbar_wait(bar(C::kBarVFull + vs), vph, w, kBSiteMmaDO))) break;
         issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColDp, doa,
                                    smem_base + C::kOffV + vs * T::kTileBytes);
         commit(C::kBarDpFull);
-        commit(C::kBarVEmpty + vs);
+        commit(C::kBarVEmpty + vs);  // V is free once dP has read it
+        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 1);
         if (++vs == C::kVStages) {
           vs = 0;
           vph ^= 1;
         }
-        return true;
+      }
+    } else if (warp == C::kMmaWarp + 3) {
+      // ------------------------------------------------------------ warp Z: S(j) = Q K_j^T
+      const uint32_t elected = elect_one();
+      auto commit = [&](int b) {
+        if (elected) mma_commit(bar(b));
       };
+      const uint32_t qa = smem_base + C::kOffQ;
+      int ks = 0, kph = 0;  // ring position of the next K tile
       bool ok = mbar_wait(bar(C::kBarQ), 0, w, kBSiteMmaQ);
-      ok = ok && issue_s(0) && issue_dp();
-      if (ok && nkv > 1) ok = issue_s(1);
       for (int j = 0; ok && j < nkv; ++j) {
-        if (j + 1 < nkv) {
-          // dP columns are free once every compute warp has read dP(j)
-          if (!(ok = mbar_wait(bar(C::kBarDpConsumed), j & 1, w, kBSiteMmaDrain))) break;
+        if (j >= 2) {
+          // score buffer j%2 holds dS(j-2) until dQ += dS(j-2) K_(j-2) has completed
+          if (!(ok = mbar_wait(bar(C::kBarDqDone + (j & 1)), ((j - 2) >> 1) & 1, w, kBSiteMmaDs)))
+            break;
           tc_fence_after();
-          FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 0);
-          if (!(ok = issue_dp())) break;
-          FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 1);
         }
-        if (j + 2 < nkv) {
-          // score buffer j%2 holds dS(j) until dQ += dS(j) K_j has completed
-          if (!(ok = mbar_wait(bar(C::kBarDqDone), j & 1, w, kBSiteMmaDs))) break;
-          tc_fence_after();
-          if (!(ok = issue_s(j + 2))) break;
-          FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 4);
+        if (!(ok = mbar_wait(bar(C::kBarKFull + ks), kph, w, kBSiteMmaKV))) break;
+        issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS + (j & 1) * 128, qa,
+                                   smem_base + C::kOffK + ks * T::kTileBytes);
+        commit(C::kBarSFull + (j & 1));
+        commit(C::kBarKEmpty + ks);
+        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 4);
+        if (++ks == C::kKStages) {
+          ks = 0;
+          kph ^= 1;
         }
       }
     } else if (warp == C::kMmaWarp + 2) {
@@ -712,7 +716,7 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
         // A = 16-bit dS over score buffer j%2, B = K_j as MN-major tile
         issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDQ, tmem_base + C::kColS + (j & 1) * 128,
                                    64, smem_base + C::kOffK + ks * T::kTileBytes, j > 0);
-        commit(C::kBarDqDone);
+        commit(C::kBarDqDone + (j & 1));
         commit(C::kBarKEmpty + ks);
         FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 3);
         if (++ks == C::kKStages) {
