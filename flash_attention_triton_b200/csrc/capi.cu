@@ -60,6 +60,12 @@ int device_state(DeviceState** out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= kMaxDevices) return FA2_ERR_ARCH;
+  // cudaGetDevice alone does not make the device's primary context current in a thread that
+  // has made no other runtime call yet (a freshly started worker thread whose allocations all
+  // came from a cache); cuTensorMapEncodeTiled, a driver call, then refuses the tensor.
+  // cudaSetDevice binds the context and costs nothing when it is bound already.
+  e = cudaSetDevice(dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
   DeviceState& d = g_dev[dev];
   std::call_once(d.once, [&] {
     d.err = cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev);

@@ -286,6 +286,31 @@ def test_deterministic_mode_is_bit_identical_across_gpus():
         assert torch.equal(torch.cat(parts[key], dim=1).view_as(full[key]), full[key]), key
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_data_parallel_matches_single_gpu():
+    """The operator under nn.DataParallel (one host thread per GPU, batch split) against one GPU,
+    like tests/test_flash_attention_2.py:415-480 of the reference, with the deterministic mode
+    so that the comparison is exact instead of allclose."""
+
+    class AttentionModel(torch.nn.Module):
+        def forward(self, q, k, v):
+            return flash_attention_v2(q, k, v, None, deterministic=True)
+
+    ngpu = min(torch.cuda.device_count(), 4)
+    q, k, v, do = (t.to(DEV) for t in make_inputs((2 * ngpu, 3, 700, 64), torch.float16))
+    model = torch.nn.DataParallel(AttentionModel(), device_ids=list(range(ngpu))).to(DEV)
+    qp, kp, vp = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out_p = model(qp, kp, vp)
+    out_p.backward(do)
+    single = run_api(q, k, v, do, None, True)
+    for dev in range(ngpu):
+        with torch.cuda.device(dev):
+            assert _lib.device_status() == 0
+    assert torch.equal(out_p, single["o"])
+    for key, t in (("dq", qp), ("dk", kp), ("dv", vp)):
+        assert torch.equal(t.grad, single[key]), key
+
+
 def test_atomic_mode_matches_deterministic_mode_closely():
     """dK, dV and O do not depend on the dQ strategy (bit-equal); dQ differs only by fp32
     summation order before the single rounding."""
@@ -337,6 +362,37 @@ def test_full_size_properties_c3_shape():
     atomic = run_api(q, k, v, do, None, False)
     assert torch.equal(atomic["dk"], got["dk"]) and torch.equal(atomic["dv"], got["dv"])
     assert (atomic["dq"].float() - got["dq"].float()).abs().max() <= 2e-2
+
+
+def test_long_sequence_c4_slab():
+    """One GPU's share of the 8-GPU long-context configuration: bf16 [1,2,32768,128] (2 of the 16
+    heads), atomic dQ as that configuration asks.  256 tiles per head; checked through
+    (1) rows of the last tile and of the first tile of one head against the fp64 definition
+        (a row only needs its own q and the k, v before it, so single rows are cheap),
+    (2) |O| <= max |V|, no NaN anywhere,
+    (3) dK, dV bit-equal between the atomic and the deterministic mode, dQ close."""
+    n, d = 32768, 128
+    q, k, v, do = make_inputs((1, 2, n, d), torch.bfloat16)
+    got = run_api(q, k, v, do, None, False)
+    for key in got:
+        assert not torch.isnan(got[key]).any(), key
+    assert got["o"].abs().max().item() <= 1.01 * v.abs().max().item()
+    scale = 1.0 / math.sqrt(d)
+    for row in (0, 127, 128, 20000, n - 129, n - 1):
+        qr = q[0, 1, row].double()
+        s = (k[0, 1, : row + 1].double() @ qr) * scale
+        p = torch.softmax(s, dim=0)
+        want = p @ v[0, 1, : row + 1].double()
+        err = (got["o"][0, 1, row].cpu().double() - want).abs().max().item()
+        assert err <= 2e-2, (row, err)
+    det = run_api(q, k, v, do, None, True)
+    assert torch.equal(det["o"], got["o"])
+    assert torch.equal(det["dk"], got["dk"]) and torch.equal(det["dv"], got["dv"])
+    assert (det["dq"].float() - got["dq"].float()).abs().max() <= 2e-2
+    # dV of the last key row: only the last query sees it, with probability p_last
+    p_last = torch.softmax((k[0, 1].double() @ q[0, 1, n - 1].double()) * scale, dim=0)[n - 1]
+    want_dv = p_last * do[0, 1, n - 1].double()
+    assert (got["dv"][0, 1, n - 1].cpu().double() - want_dv).abs().max() <= 2e-2
 
 
 def test_ragged_peaked_c5_shape_is_repeatable():
