@@ -19,6 +19,9 @@ Printed JSON (one line, rank 0):
   roofline     tensor-core roofline of the dominant kernel (backward main), achieved = its
                algorithmic FLOPs / its own average launch duration (CUDA events around that
                launch), peak = MEASURED_PEAKS.json bf16_tflops (burst; kernel timed alone).
+  sustained    the same device-resident step run back to back for about a second under the
+               clock sampler (the timed region is too short for NVML's clock averaging):
+               steps, ms_per_step, value and the clocks / throttle reasons seen.
   cpu_baseline naive fp32 PyTorch causal attention fwd+bwd on the host cores over a bounded
                sample of the same workload's heads (rank 0, N=1 only).
 
@@ -217,6 +220,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--sustain-seconds", type=float, default=1.0,
+                    help="extra untimed-for-the-metric run of the same step under the clock sampler")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -324,6 +329,26 @@ def main():
     ms_per_step = ms_total / args.steps
     value = 3.5 * total_fwd_flops / (ms_per_step * 1e-3) / 1e12
 
+    # ------------------------------------------------------------ the same step, sustained
+    # The timed region lasts tens of milliseconds, shorter than NVML's clock averaging, so its
+    # clock samples mostly show the idle clock.  Run the same step back to back for about a
+    # second under the sampler: this is where the power cap and the clock it settles at show.
+    sustained = None
+    if args.sustain_seconds > 0:
+        n_sus = max(args.steps, int(args.sustain_seconds * 1e3 / ms_per_step))
+        barrier()
+        with ClockSampler(local_rank) as sus_clocks:
+            ev0.record()
+            for _ in range(n_sus):
+                step()
+            ev1.record()
+            torch.cuda.synchronize()
+        barrier()
+        sus_ms = max_over_ranks(ev0.elapsed_time(ev1)) / n_sus
+        sustained = {"steps": n_sus, "ms_per_step": sus_ms,
+                     "value": 3.5 * total_fwd_flops / (sus_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                     "clocks": sus_clocks.summary()}
+
     # ------------------------------------------------------------ per-kernel breakdown
     def time_kernel(fn):
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
@@ -430,6 +455,7 @@ def main():
                              "sustained": value / world / peaks["bf16_sustained"],
                              "nominal_2250": value / world / 2250.0, "source": peaks["source"]},
             "clocks": clocks.summary(),
+            "sustained": sustained,
             "gpu_launches": 4 * args.steps,
             "roofline": roofline,
             "e2e": e2e,
