@@ -62,14 +62,16 @@ METRIC = "causal attn fwd+bwd TFLOP/s, bf16 N=8192 d=128"
 
 # DRAM bytes (read + write) of the backward-main kernels measured by ncu on the reduced C3
 # workload (24 batch*head problems, N=8192, d=128): fused kernel 303.7 + 159.2 MB; the
-# deterministic pair 203.2 + 76.1 MB (dK/dV) plus 202.9 + 37.9 MB (dQ).
-NCU_BWD_DRAM_MB_PER_24 = {False: 303.7 + 159.2, True: 203.2 + 76.1 + 202.9 + 37.9}
+# recompute pair 203.2 + 76.1 MB (dK/dV) plus 202.9 + 37.9 MB (dQ); the spill pair
+# 208.2 + 1679.1 MB (dK/dV, writes the dS tiles) plus 1686.1 + 51.8 MB (dQ, reads them back).
+NCU_BWD_DRAM_MB_PER_24 = {0: 303.7 + 159.2, 1: 203.2 + 76.1 + 202.9 + 37.9,
+                          2: 208.2 + 1679.1 + 1686.1 + 51.8}
 
 
-def traffic_bytes(d, det, batch_heads, n=8192):
-    if d != 128 or n != 8192:
+def traffic_bytes(d, mode, batch_heads, n=8192):
+    if d != 128 or n != 8192 or NCU_BWD_DRAM_MB_PER_24[mode] is None:
         return None
-    return NCU_BWD_DRAM_MB_PER_24[bool(det)] * 1e6 * batch_heads / 24.0
+    return NCU_BWD_DRAM_MB_PER_24[mode] * 1e6 * batch_heads / 24.0
 
 
 def fwd_flops(b, h, n, d):
@@ -198,12 +200,16 @@ def run_reference_arm(args, rank, world):
 
 
 def workload_config(args, wl, world):
+    from flash_attention_triton_b200 import api
+
     b, h, n, d, dtype, qk_mul, scale = wl
     return {
         "workload": f"{args.workload}: causal self-attention fwd+bwd, q,k,v,dO [B={b},H={h},N={n},d={d}] "
                     f"{str(dtype)[6:]}, iid N(0,{qk_mul:g}) q,k / N(0,1) v,dO, scale "
                     f"{scale if scale else '1/sqrt(d)'}",
         "deterministic": bool(args.deterministic),
+        "bwd_mode": args.bwd_mode or ("atomic", "recompute", "spill")[
+            api._backward_mode(bool(args.deterministic), d, n)],
         "batch_heads_per_gpu": b * h if args.scaling == "weak" else f"{b * h}/{world}",
         "l2": "inputs (4 x %.0f MB per step) exceed the 126 MB L2; no explicit flush" % (b * h * n * d * 2 / 1e6),
     }
@@ -217,6 +223,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--deterministic", action="store_true")
+    ap.add_argument("--bwd-mode", default="", choices=["", "atomic", "recompute", "spill"],
+                    help="force a dQ strategy instead of the one the API picks")
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -235,7 +243,7 @@ def main():
 
     import torch.distributed as dist
 
-    from flash_attention_triton_b200 import _lib, flash_attention_v2, shard_slab
+    from flash_attention_triton_b200 import _lib, api, flash_attention_v2, shard_slab
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -248,6 +256,10 @@ def main():
     scale = scale_opt or 1.0 / math.sqrt(d)
     code = 0 if dtype == torch.float16 else 1
     det = int(args.deterministic)
+    # dQ strategy: what flash_attention_v2(..., deterministic=args.deterministic) would pick
+    # (0 atomic, 1 recompute, 2 spill), unless --bwd-mode names one.
+    mode = ({"atomic": 0, "recompute": 1, "spill": 2}[args.bwd_mode] if args.bwd_mode
+            else api._backward_mode(bool(det), d, n))
 
     # Inputs: seeded on the CPU, then moved.  weak: each rank its own seed, whole shape.
     # strong: one global tensor (seed 0), each rank takes its contiguous (batch, head) slab.
@@ -264,7 +276,7 @@ def main():
     o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
     lse = torch.empty(lb, lh, n, device=dev, dtype=torch.float32)
     rowstats = torch.empty(lib.fa2_rowstats_bytes(lb, lh, n) // 4, device=dev, dtype=torch.float32)
-    wsb = lib.fa2_bwd_workspace_bytes(lb, lh, n, d, det)
+    wsb = lib.fa2_bwd_workspace_bytes(lb, lh, n, d, mode)
     ws = torch.empty(max(wsb // 4, 4), device=dev, dtype=torch.float32)
     stream = torch.cuda.current_stream().cuda_stream
 
@@ -280,7 +292,7 @@ def main():
         _lib.check("fa2_bwd", lib.fa2_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), rowstats.data_ptr(),
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr() if wsb else None,
-            lb, lh, n, d, code, scale, det, stream))
+            lb, lh, n, d, code, scale, mode, stream))
 
     def step():
         k_fwd()
@@ -329,26 +341,6 @@ def main():
     ms_per_step = ms_total / args.steps
     value = 3.5 * total_fwd_flops / (ms_per_step * 1e-3) / 1e12
 
-    # ------------------------------------------------------------ the same step, sustained
-    # The timed region lasts tens of milliseconds, shorter than NVML's clock averaging, so its
-    # clock samples mostly show the idle clock.  Run the same step back to back for about a
-    # second under the sampler: this is where the power cap and the clock it settles at show.
-    sustained = None
-    if args.sustain_seconds > 0:
-        n_sus = max(args.steps, int(args.sustain_seconds * 1e3 / ms_per_step))
-        barrier()
-        with ClockSampler(local_rank) as sus_clocks:
-            ev0.record()
-            for _ in range(n_sus):
-                step()
-            ev1.record()
-            torch.cuda.synchronize()
-        barrier()
-        sus_ms = max_over_ranks(ev0.elapsed_time(ev1)) / n_sus
-        sustained = {"steps": n_sus, "ms_per_step": sus_ms,
-                     "value": 3.5 * total_fwd_flops / (sus_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                     "clocks": sus_clocks.summary()}
-
     # ------------------------------------------------------------ per-kernel breakdown
     def time_kernel(fn):
         evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
@@ -369,11 +361,12 @@ def main():
     fwd_tf = my_fwd_flops / (ms_fwd * 1e-3) / 1e12
     pre_bytes = 2.0 * lb * lh * n * d * 2 + lb * lh * n * 4 * 3
     roofline = {
-        "kernel": "bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert" if not det
-                  else "bwd_dkdv_kernel + bwd_dq_kernel",
+        "kernel": ("bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert",
+                   "bwd_dkdv_kernel + bwd_dq_kernel (S, dP recomputed)",
+                   "bwd_dkdv_kernel (dS tiles spilled) + bwd_dq_spill_kernel")[mode],
         "bound": "tensor", "achieved": bwd_tf, "peak": peaks["bf16"], "unit": "TFLOP/s",
         "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} burst bf16 GEMM",
-        "traffic": traffic_bytes(d, det, lb * lh, n),
+        "traffic": traffic_bytes(d, mode, lb * lh, n),
         "traffic_note": "dram__bytes_read+write per launch(es) of the backward-main kernel(s) from the "
                         "ncu capture in profiles/attention_kernels_c3small_ncu.md (24 batch*head "
                         "problems, d=128, N=8192), scaled by batch*head; null for other shapes",
@@ -439,6 +432,26 @@ def main():
         nbytes = q.numel() * q.element_size()
         e2e = {"value": 3.5 * total_fwd_flops / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                "ms_per_step": e_ms, "h2d_bytes_per_step": 4 * nbytes, "d2h_bytes_per_step": 4 * nbytes}
+
+    # ------------------------------------------------------------ the same step, sustained
+    # The timed region lasts tens of milliseconds, shorter than NVML's clock averaging, so its
+    # clock samples mostly show the idle clock.  Run the same step back to back for about a
+    # second under the sampler: this is where the power cap and the clock it settles at show.
+    sustained = None
+    if args.sustain_seconds > 0:
+        n_sus = max(args.steps, int(args.sustain_seconds * 1e3 / ms_per_step))
+        barrier()
+        with ClockSampler(local_rank) as sus_clocks:
+            ev0.record()
+            for _ in range(n_sus):
+                step()
+            ev1.record()
+            torch.cuda.synchronize()
+        barrier()
+        sus_ms = max_over_ranks(ev0.elapsed_time(ev1)) / n_sus
+        sustained = {"steps": n_sus, "ms_per_step": sus_ms,
+                     "value": 3.5 * total_fwd_flops / (sus_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                     "clocks": sus_clocks.summary()}
 
     st = _lib.device_status()
     if st != 0:

@@ -23,6 +23,7 @@ Everything runs through the C library on the tensors' CUDA device; there is no f
 from __future__ import annotations
 
 import math
+import os
 from collections.abc import Callable
 from dataclasses import dataclass
 from typing import Any
@@ -100,6 +101,32 @@ def _flash_attention_forward(
     return output, lse, softmax_scale
 
 
+#: dQ strategies of the C library (the ``deterministic`` argument of ``fa2_bwd``)
+_MODE_ATOMIC, _MODE_RECOMPUTE, _MODE_SPILL = 0, 1, 2
+#: the spill mode keeps 32 KiB per tile pair; beyond this much per head it is not used
+_SPILL_MAX_BYTES_PER_HEAD = 2 << 30
+
+
+def _backward_mode(deterministic: bool, headdim: int, seqlen_q: int) -> int:
+    """Which dQ strategy serves ``deterministic``.
+
+    ``True`` must give the same bits whatever the batch / head partitioning, so the choice
+    depends on the sequence length only: the spill mode (fastest deterministic one) unless its
+    scratch per head is too large, then the recompute mode.  ``False`` (the reference's
+    default, atomics there) means "fastest": the spill mode where it beats the atomic kernel
+    (head dims above 64), the atomic kernel elsewhere.  ``FA2_B200_BWD_MODE`` = ``atomic`` /
+    ``recompute`` / ``spill`` overrides both (for experiments).
+    """
+    forced = os.environ.get("FA2_B200_BWD_MODE")
+    if forced:
+        return {"atomic": _MODE_ATOMIC, "recompute": _MODE_RECOMPUTE, "spill": _MODE_SPILL}[forced]
+    tiles = (seqlen_q + 127) // 128
+    spill_ok = tiles * (tiles + 1) // 2 * 32768 <= _SPILL_MAX_BYTES_PER_HEAD
+    if deterministic:
+        return _MODE_SPILL if spill_ok else _MODE_RECOMPUTE
+    return _MODE_SPILL if spill_ok and headdim > 64 else _MODE_ATOMIC
+
+
 def _flash_attention_backward(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -115,9 +142,10 @@ def _flash_attention_backward(
 ) -> None:
     """Launch ``fa2_bwd_preprocess`` and ``fa2_bwd``.
 
-    Counterpart of ``_flash_attention_backward`` (reference lines 147-277).  The fp32
-    ``dq_accum`` workspace exists only in the non-deterministic mode; the deterministic mode
-    writes dQ once, already rounded.
+    Counterpart of ``_flash_attention_backward`` (reference lines 147-277).  The workspace
+    behind ``dq_accum`` depends on the dQ strategy (:func:`_backward_mode`): an fp32 accumulator
+    for the atomic kernel, the dS scratch for the spill mode, nothing for the recompute mode;
+    the two deterministic modes write dQ once, already rounded.
     """
     batch, nheads, seqlen_q, headdim = q.shape
     seqlen_k = k.shape[2]
@@ -145,7 +173,8 @@ def _flash_attention_backward(
                 _stream(q),
             ),
         )
-        ws_bytes = lib.fa2_bwd_workspace_bytes(batch, nheads, seqlen_q, headdim, int(deterministic))
+        mode = _backward_mode(bool(deterministic), headdim, seqlen_q)
+        ws_bytes = lib.fa2_bwd_workspace_bytes(batch, nheads, seqlen_q, headdim, mode)
         dq_accum = (
             torch.empty(ws_bytes // 4, device=q.device, dtype=torch.float32) if ws_bytes else None
         )
@@ -156,7 +185,7 @@ def _flash_attention_backward(
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
                 dq_accum.data_ptr() if dq_accum is not None else None,
                 batch, nheads, seqlen_q, seqlen_k, headdim, code, float(softmax_scale),
-                int(deterministic), _lib.stride_array(q, k, v, d_output, dq, dk, dv), _stream(q),
+                mode, _lib.stride_array(q, k, v, d_output, dq, dk, dv), _stream(q),
             ),
         )
 

@@ -94,9 +94,22 @@ __device__ __forceinline__ void store_rows_16bit(uint32_t tmem_row_addr, uint8_t
 // =========================================================================================
 // dK / dV (+ fused dQ) kernel
 // =========================================================================================
-template <int D, bool FUSE>
+// Number of (KV tile, Q tile) pairs of one head whose KV tile index is below `jt`, with
+// `ntiles` Q tiles: KV tile t meets Q tiles t .. ntiles-1.  Also the index of the first pair
+// of KV tile jt in the dS scratch tensor of the spill mode.
+__host__ __device__ __forceinline__ int dstile_count(int ntiles, int jt) {
+  return jt * ntiles - jt * (jt - 1) / 2;
+}
+
+// MODE 0: dK, dV only (dQ comes from bwd_dq_kernel).  MODE 1 (fused): also dQ, accumulated into
+// an fp32 buffer with atomic adds by a fourth warp group.  MODE 2 (spill): also stores every
+// 16-bit dS^T tile to a scratch tensor (dq_accum then points to it), from which
+// bwd_dq_spill_kernel forms dQ with one product per tile pair instead of recomputing S, P, dP.
+template <int D, int MODE>
 struct DkdvCfg {
   using T = Tile<D>;
+  static constexpr bool FUSE = MODE == 1;
+  static constexpr bool SPILL = MODE == 2;
   static constexpr int kStages = 2;  // Q (+rowstats) ring and dO ring (the code relies on 2)
   static constexpr int kThreads = FUSE ? 512 : 384;
   static constexpr int kMmaWarp = FUSE ? 12 : 8;
@@ -122,6 +135,7 @@ struct DkdvCfg {
   static constexpr int kBarDone = kBarDqDrained + 1;
   static constexpr int kNumBars = kBarDone + 1;
   static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
+  static_assert(kSmemBytes <= 232448, "shared memory budget of one CTA");
   static constexpr int kColSt = 0;
   static constexpr int kColDpt = 128;  // dQ (fused) reuses these columns
   static constexpr int kColDV = 256;
@@ -146,15 +160,17 @@ enum BwdSite {
   kBSiteAlign
 };
 
-template <int D, bool BF16, bool FUSE>
-__global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
+template <int D, bool BF16, int MODE>
+__global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
     bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                     const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo,
                     const __grid_constant__ CUtensorMap tdk,
                     const __grid_constant__ CUtensorMap tdv, const float* __restrict__ rowstats,
                     float* __restrict__ dq_accum, int N, int Nk, float scale, float scale_log2,
                     int* status) {
-  using C = DkdvCfg<D, FUSE>;
+  using C = DkdvCfg<D, MODE>;
+  constexpr bool FUSE = C::FUSE;
+  constexpr bool SPILL = C::SPILL;
   using T = Tile<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
   // Role index: the producer / MMA group takes hardware warps 0-3 (lowest ids on their
@@ -178,6 +194,10 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
   const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
   const int nq = ntiles - jt;  // Q tiles jt .. ntiles-1 (N = query rows, Nk <= N = key rows)
   const bool kv_ragged = jt * 128 + 128 > Nk;  // this KV tile has rows beyond the last key
+  // Spill mode: tiles of a head are numbered KV tile by KV tile, Q tiles ascending inside.
+  const int nktiles = (Nk + 127) >> 7;
+  const int tile0 = bh * dstile_count(ntiles, nktiles) + dstile_count(ntiles, jt);
+  (void)tile0;
   const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;  // FA2_TRACE_EVENT only
   (void)traced;
 
@@ -462,6 +482,19 @@ __global__ void __launch_bounds__(DkdvCfg<D, FUSE>::kThreads, 1)
         }
       }
       tmem_st_x32(tDpt, dsk);  // columns 128 + wg*64 .. +31
+      if constexpr (SPILL) {
+        // This thread's 64 values of dS^T(jt, jt+ii) (kv row r, q columns wg*64 ..) straight to
+        // pair `tile0 + ii` of the scratch tensor.  A tile is stored piece-major: the 16-byte
+        // piece (kv row r, q columns 8g .. 8g+7) at byte g * 2048 + r * 16, so one warp
+        // instruction writes 512 contiguous bytes, and the tile can later be copied linearly
+        // into shared memory as an unswizzled tensor-core operand.  Going through registers
+        // keeps the copy out of shared memory, whose bandwidth the operand reads already use up.
+        uint4* dst = reinterpret_cast<uint4*>(dq_accum) +
+                     (static_cast<size_t>(tile0 + ii) * 2048 + wg * 1024 + r);
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc)
+          dst[pc * 128] = make_uint4(dsk[4 * pc], dsk[4 * pc + 1], dsk[4 * pc + 2], dsk[4 * pc + 3]);
+      }
       if constexpr (FUSE) {
         uint8_t* ds_tile = smem + C::kOffDS + wg * 16384;
 #pragma unroll
@@ -813,13 +846,136 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
   }
 }
 
-template <int D, bool BF16, bool FUSE>
+// =========================================================================================
+// dQ from spilled dS tiles (spill mode).  CTA = one Q tile; dQ = sum_j dS(j)^T-tile^T K_j in
+// ascending KV order, one tensor-core product per KV tile, no exponentials: the kernel is
+// bound by reading the 32 KiB dS tile per product from HBM.
+//   warps 0-3  epilogue (dQ: tensor memory -> 16 bit -> TMA store)
+//   warp  4    TMA producer: ring of kStages x (dS^T tile + K tile)
+//   warp  5    MMA issue
+// =========================================================================================
+template <int D>
+struct DqSpillCfg {
+  using T = Tile<D>;
+  static constexpr int kStages = D == 128 ? 3 : 4;
+  static constexpr int kThreads = 192;
+  static constexpr int kLoadWarp = 4;
+  static constexpr int kMmaWarp = 5;
+  static constexpr int kStageBytes = 32768 + T::kTileBytes;  // dS^T tile, then the K tile
+  static constexpr int kOffBar = kStages * kStageBytes;
+  static constexpr int kBarFull = 0;
+  static constexpr int kBarEmpty = kStages;
+  static constexpr int kBarDone = 2 * kStages;
+  static constexpr int kNumBars = kBarDone + 1;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
+  static constexpr int kTmemCols = D < 32 ? 32 : D;
+  static_assert(kSmemBytes <= 232448, "shared memory budget of one CTA");
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(DqSpillCfg<D>::kThreads, 1)
+    bwd_dq_spill_kernel(const uint4* __restrict__ ds_scratch,
+                        const __grid_constant__ CUtensorMap tk,
+                        const __grid_constant__ CUtensorMap tdq, int N, int Nk, int* status) {
+  using C = DqSpillCfg<D>;
+  using T = Tile<D>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  if (smem_base & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, 0x20000 | kBSiteAlign);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_base + C::kOffBar + 8u * i; };
+
+  const int ntiles = (N + 127) >> 7;
+  const int nktiles = (Nk + 127) >> 7;
+  const int qt = ntiles - 1 - static_cast<int>(blockIdx.x);  // heaviest Q tile first
+  const HeadCoord hc{static_cast<int>(blockIdx.y), static_cast<int>(blockIdx.z)};  // grid (tiles, H, B)
+  const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
+  const int nkv = qt + 1 < nktiles ? qt + 1 : nktiles;
+  const int head_tile0 = bh * dstile_count(ntiles, nktiles);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < C::kStages; ++i) {
+      mbar_init(bar(C::kBarFull + i), 1);
+      mbar_init(bar(C::kBarEmpty + i), 1);
+    }
+    mbar_init(bar(C::kBarDone), 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == C::kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtx w{abort_flag, status};
+
+  if (warp == C::kLoadWarp) {
+    const uint32_t elected = elect_one();
+    if (elected) prefetch_tensormap(&tk);
+    for (int j = 0; j < nkv; ++j) {
+      const int st = j % C::kStages, ph = (j / C::kStages) & 1;
+      if (!mbar_wait_warp(bar(C::kBarEmpty + st), ph ^ 1, w, kBSiteLoadQ)) break;
+      if (elected) {
+        const uint32_t dst = smem_base + st * C::kStageBytes;
+        const int tile = head_tile0 + dstile_count(ntiles, j) + (qt - j);  // pair (KV j, Q qt)
+        mbar_arrive_expect_tx(bar(C::kBarFull + st), C::kStageBytes);
+        bulk_load_1d(dst, ds_scratch + static_cast<size_t>(tile) * 2048, 32768,
+                     bar(C::kBarFull + st));  // a tile is 32 KiB, stored as it is used
+#pragma unroll
+        for (int ch = 0; ch < T::kChunks; ++ch)
+          tma_load_4d(dst + 32768 + ch * T::kChunkTileBytes, &tk, ch * T::kChunkElems, j * 128, hc,
+                      bar(C::kBarFull + st));
+      }
+    }
+    __syncwarp();
+  } else if (warp == C::kMmaWarp) {
+    const uint32_t elected = elect_one();
+    bool ok = true;
+    for (int j = 0; ok && j < nkv; ++j) {
+      const int st = j % C::kStages, ph = (j / C::kStages) & 1;
+      if (!(ok = mbar_wait(bar(C::kBarFull + st), ph, w, kBSiteMmaKV))) break;
+      const uint32_t src = smem_base + st * C::kStageBytes;
+      // dQ[128 q, D] += dS[q, kv] K[kv, d]: A = the dS^T tile (q contiguous, MN-major, piece-
+      // major unswizzled), B = the K tile (d contiguous, MN-major)
+      issue_piecesT_x_tile<D, BF16>(elected, tmem_base, src, src + 32768, j > 0);
+      if (elected) mma_commit(bar(C::kBarEmpty + st));
+    }
+    if (ok && elected) mma_commit(bar(C::kBarDone));
+    __syncwarp();
+  } else {
+    if (mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
+      tc_fence_after();
+      const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+      // every product has completed, so the ring is idle: stage through its first buffer
+      store_rows_16bit<D, BF16>(tmem_base + lane_base, smem, warp, lane, &tdq, qt * 128, hc, N);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == C::kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int D, bool BF16, int MODE>
 cudaError_t launch_dkdv_t(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                           const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdk,
                           const CUtensorMap& tdv, const float* rowstats, float* dq_accum,
                           int* status, cudaStream_t stream) {
-  using C = DkdvCfg<D, FUSE>;
-  auto kern = bwd_dkdv_kernel<D, BF16, FUSE>;
+  using C = DkdvCfg<D, MODE>;
+  auto kern = bwd_dkdv_kernel<D, BF16, MODE>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
@@ -827,6 +983,20 @@ cudaError_t launch_dkdv_t(const AttnShape& s, const CUtensorMap& tq, const CUten
   kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum,
                                                      s.N, s.Nk, s.scale,
                                                      s.scale * 1.4426950408889634f, status);
+  return cudaGetLastError();
+}
+
+template <int D, bool BF16>
+cudaError_t launch_dq_spill_t(const AttnShape& s, const void* ds_scratch, const CUtensorMap& tk,
+                              const CUtensorMap& tdq, int* status, cudaStream_t stream) {
+  using C = DqSpillCfg<D>;
+  auto kern = bwd_dq_spill_kernel<D, BF16>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  dim3 grid((s.N + 127) / 128, s.H, s.B);
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(static_cast<const uint4*>(ds_scratch), tk, tdq,
+                                                     s.N, s.Nk, status);
   return cudaGetLastError();
 }
 
@@ -858,16 +1028,21 @@ extern "C" int fa2_trace_read_bwd(long long* out, int n) {
 cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                             const CUtensorMap& tv, const CUtensorMap& tdo,
                             const CUtensorMap& tdk, const CUtensorMap& tdv,
-                            const float* rowstats, float* dq_accum, int fuse_dq, int* status,
+                            const float* rowstats, float* dq_accum, int mode, int* status,
                             cudaStream_t stream) {
+  // modes: 0 dK/dV only, 1 fused atomic dQ (dq_accum = fp32 accumulator), 2 spill dS tiles
+  // (dq_accum = the 16-bit scratch tensor)
 #define FA2_ARGS s, tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum, status, stream
 #define FA2_CASE(DD)                                                                        \
   case DD:                                                                                  \
-    if (fuse_dq)                                                                            \
-      return s.dtype ? launch_dkdv_t<DD, true, true>(FA2_ARGS)                              \
-                     : launch_dkdv_t<DD, false, true>(FA2_ARGS);                            \
-    return s.dtype ? launch_dkdv_t<DD, true, false>(FA2_ARGS)                               \
-                   : launch_dkdv_t<DD, false, false>(FA2_ARGS);
+    if (mode == 1)                                                                          \
+      return s.dtype ? launch_dkdv_t<DD, true, 1>(FA2_ARGS)                                 \
+                     : launch_dkdv_t<DD, false, 1>(FA2_ARGS);                               \
+    if (mode == 2)                                                                          \
+      return s.dtype ? launch_dkdv_t<DD, true, 2>(FA2_ARGS)                                 \
+                     : launch_dkdv_t<DD, false, 2>(FA2_ARGS);                               \
+    return s.dtype ? launch_dkdv_t<DD, true, 0>(FA2_ARGS)                                   \
+                   : launch_dkdv_t<DD, false, 0>(FA2_ARGS);
   switch (s.D) {
     FA2_CASE(32)
     FA2_CASE(64)
@@ -893,6 +1068,21 @@ cudaError_t launch_bwd_dq(const AttnShape& s, const CUtensorMap& tq, const CUten
   }
 #undef FA2_CASE
 #undef FA2_ARGS
+  return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_bwd_dq_spill(const AttnShape& s, const void* ds_scratch, const CUtensorMap& tk,
+                                const CUtensorMap& tdq, int* status, cudaStream_t stream) {
+#define FA2_CASE(DD)                                                                         \
+  case DD:                                                                                   \
+    return s.dtype ? launch_dq_spill_t<DD, true>(s, ds_scratch, tk, tdq, status, stream)     \
+                   : launch_dq_spill_t<DD, false>(s, ds_scratch, tk, tdq, status, stream);
+  switch (s.D) {
+    FA2_CASE(32)
+    FA2_CASE(64)
+    FA2_CASE(128)
+  }
+#undef FA2_CASE
   return cudaErrorInvalidValue;
 }
 

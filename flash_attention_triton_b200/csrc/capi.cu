@@ -1,6 +1,7 @@
 // C ABI of the library (declared in include/fa2_b200.h): argument validation, tensor-map
 // construction and kernel dispatch.  Nothing here allocates device memory or synchronises,
 // except fa2_device_status which reads the status word back.
+#include <algorithm>
 #include <atomic>
 #include <cmath>
 #include <cstdint>
@@ -153,6 +154,23 @@ int check_shape(int B, int H, int N, int D, int dtype) {
   return FA2_OK;
 }
 
+// Spill mode (deterministic == 2): the dS scratch is bounded by working through the problem in
+// chunks of whole batch entries, or of head ranges of one batch entry when a single entry is
+// already too large.  The split never changes a bit of the results (every (batch, head)
+// problem is independent); it depends on H and N only.
+std::atomic<long long> g_spill_budget{8ll << 30};
+struct SpillPlan {
+  int nb, nh;  // batch entries and heads per chunk
+};
+SpillPlan spill_plan(int B, int H, int N) {
+  const long long per_head = dstile_pairs(N, N) * 32768;
+  const long long heads_fit = std::max<long long>(1, g_spill_budget.load() / per_head);
+  if (heads_fit >= H)
+    return SpillPlan{static_cast<int>(std::min<long long>(B, std::max<long long>(1, heads_fit / H))), H};
+  const long long nchunks = (H + heads_fit - 1) / heads_fit;
+  return SpillPlan{1, static_cast<int>((H + nchunks - 1) / nchunks)};
+}
+
 AttnShape make_shape(int B, int H, int N, int Nk, int D, int dtype, float scale) {
   return AttnShape{B, H, N, padded_head_dim(D), dtype, scale, D, Nk};
 }
@@ -247,7 +265,11 @@ int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float*
 }
 
 size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
-  if (deterministic || B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
+  if (deterministic == 1 || B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
+  if (deterministic == 2) {  // one 16-bit [128 x 128] dS tile per (KV tile, Q tile) pair of a chunk
+    const SpillPlan plan = spill_plan(B, H, N);
+    return static_cast<size_t>(plan.nb) * plan.nh * static_cast<size_t>(dstile_pairs(N, N)) * 32768;
+  }
   const size_t ntiles = (static_cast<size_t>(N) + 127) / 128;
   return static_cast<size_t>(B) * H * ntiles * 128 * padded_head_dim(D) * sizeof(float);
 }
@@ -263,8 +285,9 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
       !aligned16(dk) || !aligned16(dv) || !aligned16(rowstats))
     return FA2_ERR_MISALIGNED;
   if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
-  if (!deterministic && !dq_accum) return FA2_ERR_WORKSPACE;
-  if (!deterministic && !aligned16(dq_accum)) return FA2_ERR_MISALIGNED;
+  if (deterministic < 0 || deterministic > 2) return FA2_ERR_SHAPE;
+  if (deterministic != 1 && !dq_accum) return FA2_ERR_WORKSPACE;
+  if (deterministic != 1 && !aligned16(dq_accum)) return FA2_ERR_MISALIGNED;
   const int rows_of[7] = {N, Nk, Nk, N, N, Nk, Nk};  // q, k, v, dout, dq, dk, dv
   for (int idx = 0; idx < 7; ++idx) {
     Strides unused;
@@ -283,12 +306,52 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
   Strides sdq;
   if (int e = get_strides(strides, 4, B, H, N, D, &sdq)) return e;
   const AttnShape s = make_shape(B, H, N, Nk, D, dtype, scale);
-  if (deterministic) {
+  if (deterministic == 1) {
     if (int e = make_map(&tdq, dq, dtype, B, H, N, D, sdq, 32)) return e;
     cudaError_t ce =
         launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, nullptr, 0, d->status, st);
     if (ce != cudaSuccess) return static_cast<int>(ce);
     return static_cast<int>(launch_bwd_dq(s, tq, tk, tv, tdo, tdq, rowstats, d->status, st));
+  }
+  if (deterministic == 2) {
+    const SpillPlan plan = spill_plan(B, H, N);
+    if (plan.nb < B || plan.nh < H) {
+      // more than one chunk: the same call on sub-ranges, one after the other on the stream
+      // (they share the scratch), with the caller's strides spelled out
+      const void* in[4] = {q, k, v, dout};
+      void* out[3] = {dq, dk, dv};
+      long long st_all[21];
+      const int rows_of2[7] = {N, Nk, Nk, N, N, Nk, Nk};
+      for (int idx = 0; idx < 7; ++idx) {
+        Strides t;
+        if (int e = get_strides(strides, idx, B, H, rows_of2[idx], D, &t)) return e;
+        st_all[3 * idx] = t.b, st_all[3 * idx + 1] = t.h, st_all[3 * idx + 2] = t.n;
+      }
+      const size_t stats_per_head = fa2_rowstats_bytes(1, 1, N) / sizeof(float);
+      for (int b0 = 0; b0 < B; b0 += plan.nb)
+        for (int h0 = 0; h0 < H; h0 += plan.nh) {
+          const int nb = std::min(plan.nb, B - b0), nh = std::min(plan.nh, H - h0);
+          auto at = [&](const void* p, int idx) {
+            return static_cast<const char*>(p) + 2 * (b0 * st_all[3 * idx] + h0 * st_all[3 * idx + 1]);
+          };
+          const int e = fa2_bwd_strided(
+              at(in[0], 0), at(in[1], 1), at(in[2], 2), at(in[3], 3),
+              rowstats + (static_cast<size_t>(b0) * H + h0) * stats_per_head,
+              const_cast<char*>(at(out[0], 4)), const_cast<char*>(at(out[1], 5)),
+              const_cast<char*>(at(out[2], 6)), dq_accum, nb, nh, N, Nk, D, dtype, scale, 2, st_all,
+              stream);
+          if (e) return e;
+        }
+      return FA2_OK;
+    }
+    // dS scratch: one 32 KiB tile per (KV tile, Q tile) pair
+    const long long pairs = static_cast<long long>(B) * H * dstile_pairs(N, Nk);
+    if (pairs >= (1ll << 31)) return FA2_ERR_SHAPE;
+    if (int e = make_map(&tdq, dq, dtype, B, H, N, D, sdq, 32)) return e;
+    cudaError_t ce =
+        launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum, 2, d->status, st);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+    return static_cast<int>(launch_bwd_dq_spill(s, dq_accum, tk, tdq, d->status, st));
   }
   cudaError_t ce = cudaMemsetAsync(dq_accum, 0, fa2_bwd_workspace_bytes(B, H, N, D, 0), st);
   if (ce != cudaSuccess) return static_cast<int>(ce);
@@ -302,6 +365,10 @@ int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const
             float scale, int deterministic, fa2_stream_t stream) {
   return fa2_bwd_strided(q, k, v, dout, rowstats, dq, dk, dv, dq_accum, B, H, N, N, D, dtype,
                          scale, deterministic, nullptr, stream);
+}
+
+size_t fa2_set_spill_budget(size_t bytes) {
+  return static_cast<size_t>(g_spill_budget.exchange(static_cast<long long>(bytes)));
 }
 
 int fa2_device_status(int* status_out) {

@@ -96,14 +96,26 @@ cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strid
                                   const void* dout, const Strides& sdo, const float* lse,
                                   float* rowstats, cudaStream_t stream);
 
-// dK/dV per KV tile.  fuse_dq != 0 also accumulates dQ into dq_accum with fp32 atomic adds.
-// dq_accum layout: [bh][t][w = 4][k = D/4][lane = 32][4] floats, holding element
-// (row 128*t + 32*w + lane, col 4*k + 0..3).
+// dK/dV per KV tile.  mode 1 also accumulates dQ into dq_accum with fp32 atomic adds
+// (dq_accum layout: [bh][t][w = 4][k = D/4][lane = 32][4] floats, holding element
+// (row 128*t + 32*w + lane, col 4*k + 0..3)); mode 2 also stores every 16-bit dS^T tile to the
+// scratch tensor dq_accum then points to (32 KiB per (KV tile, Q tile) pair, pairs numbered
+// per head KV tile by KV tile, see dstile_pairs), from which launch_bwd_dq_spill forms dQ.
 cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                             const CUtensorMap& tv, const CUtensorMap& tdo,
                             const CUtensorMap& tdk, const CUtensorMap& tdv,
-                            const float* rowstats, float* dq_accum, int fuse_dq, int* status,
+                            const float* rowstats, float* dq_accum, int mode, int* status,
                             cudaStream_t stream);
+
+// dQ per Q tile from the spilled dS tiles, ascending KV order (deterministic).
+cudaError_t launch_bwd_dq_spill(const AttnShape& s, const void* ds_scratch, const CUtensorMap& tk,
+                                const CUtensorMap& tdq, int* status, cudaStream_t stream);
+
+// (KV tile, Q tile) pairs of one head: KV tile t < nktiles meets Q tiles t .. ntiles-1.
+inline long long dstile_pairs(int N, int Nk) {
+  const long long nt = (N + 127) / 128, nk = (Nk + 127) / 128;
+  return nk * nt - nk * (nk - 1) / 2;
+}
 
 // dQ per Q tile, ascending KV order (deterministic path).
 cudaError_t launch_bwd_dq(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,

@@ -64,11 +64,12 @@ __device__ __forceinline__ void issue_tmem_x_tile(uint32_t elected, uint32_t d_t
   }
 }
 
-// acc[128, D] = A^T * B with A = [128 rows (reduction), 128] 16-bit tile written by threads as
+// acc[128, D] (+)= A^T * B with A = [128 rows (reduction), 128] 16-bit tile written by threads as
 // two swizzled [128][64] chunk tiles (MN-major A) and B a staged [128, D] tile (MN-major B).
 template <int D, bool BF16>
 __device__ __forceinline__ void issue_tileT_x_tile(uint32_t elected, uint32_t d_tmem,
-                                                   uint32_t a_addr, uint32_t b_addr) {
+                                                   uint32_t a_addr, uint32_t b_addr,
+                                                   uint32_t accumulate = 0u) {
   using T = Tile<D>;
   constexpr uint32_t idesc = make_idesc(128, D, BF16, true, true);
   constexpr uint32_t a_hi = desc_hi_word(1024, kSwizzle128B);
@@ -78,7 +79,34 @@ __device__ __forceinline__ void issue_tileT_x_tile(uint32_t elected, uint32_t d_
   for (int k = 0; k < 8; ++k)
     if (elected)
       mma_ss(d_tmem, desc_from_words(a_lo + ((k * 2048) >> 4), a_hi),
-             desc_from_words(b_lo + ((k * 2 * T::kAtomBytes) >> 4), b_hi), idesc, k > 0 ? 1u : 0u);
+             desc_from_words(b_lo + ((k * 2 * T::kAtomBytes) >> 4), b_hi), idesc,
+             k > 0 ? 1u : accumulate);
+}
+
+// acc[128, D] (+)= A^T * B like issue_tileT_x_tile, but with A in the unswizzled "piece-major"
+// layout the spill mode keeps in global memory and copies linearly into shared memory:
+// element (reduction row r, column c) at byte (c / 8) * 2048 + r * 16 + (c % 8) * 2, i.e. core
+// matrices of 8 rows x 16 bytes, consecutive along the reduction rows (128 bytes apart) and
+// 2048 bytes apart along the columns.
+#ifndef FA2_NS_LBO
+#define FA2_NS_LBO 128   /* stride between core matrices along the reduction (K) index */
+#define FA2_NS_SBO 2048  /* stride between core matrices along the M index */
+#endif
+template <int D, bool BF16>
+__device__ __forceinline__ void issue_piecesT_x_tile(uint32_t elected, uint32_t d_tmem,
+                                                     uint32_t a_addr, uint32_t b_addr,
+                                                     uint32_t accumulate) {
+  using T = Tile<D>;
+  constexpr uint32_t idesc = make_idesc(128, D, BF16, true, true);
+  constexpr uint32_t a_hi = desc_hi_word(FA2_NS_SBO, 0u);  // no swizzle
+  constexpr uint32_t b_hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
+  const uint32_t a_lo = desc_lo_word(a_addr, FA2_NS_LBO), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    if (elected)
+      mma_ss(d_tmem, desc_from_words(a_lo + ((k * 256) >> 4), a_hi),
+             desc_from_words(b_lo + ((k * 2 * T::kAtomBytes) >> 4), b_hi), idesc,
+             k > 0 ? 1u : accumulate);
 }
 
 }  // namespace fa2

@@ -149,6 +149,28 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, int x, int 
       "r"(x), "r"(y), "r"(hc.h), "r"(hc.b), "r"(src_smem)
       : "memory");
 }
+// 3-D variants for the library's own dense scratch tensors: {x, y, tile index}.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const CUtensorMap* map, int x,
+                                            int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst_smem),
+      "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int x, int y, int z,
+                                             uint32_t src_smem) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];" ::"l"(
+          map),
+      "r"(x), "r"(y), "r"(z), "r"(src_smem)
+      : "memory");
+}
+// All bulk stores of this thread have finished READING shared memory (the data may still be
+// in flight to global memory): the source buffer can be rewritten.
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
 __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

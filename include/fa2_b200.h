@@ -87,9 +87,18 @@ size_t fa2_rowstats_bytes(int B, int H, int N);
 /*
  * Backward main.  Inputs q,k,v,dout and rowstats (from fa2_bwd_preprocess); outputs
  * dq,dk,dv in the input dtype.
- *   deterministic != 0: dK/dV kernel + a separate dQ kernel; every output tile has one
- *     owner and a fixed accumulation order, so results are bit-identical across runs,
- *     SM counts and (batch, head) partitionings.  dq_accum is not used (may be NULL).
+ *   deterministic == 1: dK/dV kernel + a separate dQ kernel that recomputes S and dP; every
+ *     output tile has one owner and a fixed accumulation order, so results are bit-identical
+ *     across runs, SM counts and (batch, head) partitionings.  dq_accum is not used (may be
+ *     NULL).
+ *   deterministic == 2 ("spill"): equally deterministic, and the fastest mode at D = 128.  The
+ *     dK/dV kernel also writes every 16-bit dS tile to the scratch behind dq_accum
+ *     (fa2_bwd_workspace_bytes(.., 2) bytes, bounded by fa2_set_spill_budget) and a second
+ *     kernel forms dQ from those tiles with one tensor-core product per tile pair, bound by
+ *     reading the scratch from HBM.  Trades memory (quadratic in N per head, chunked) for
+ *     time; dK and dV are bit-identical to mode 1, dQ differs from it in the last bit at most
+ *     (other polynomial / MUFU assignment of the exponentials).  No counterpart in the
+ *     reference.
  *   deterministic == 0: one fused kernel per KV tile adds its dQ contributions into the
  *     fp32 workspace dq_accum with atomic adds (the reference's SEQUENCE_PARALLEL mode,
  *     _triton_kernels_v2.py:337-339), then a convert pass writes dq, rounding once like
@@ -104,8 +113,22 @@ int fa2_bwd(const void* q, const void* k, const void* v, const void* dout,
             int B, int H, int N, int D, int dtype, float scale, int deterministic,
             fa2_stream_t stream);
 
-/* Bytes of fp32 workspace fa2_bwd needs (0 when deterministic != 0). */
+/*
+ * Bytes of workspace fa2_bwd needs behind `dq_accum` for a value of `deterministic`:
+ *   0  fp32 dQ accumulator of the atomic mode, [B*H][ceil(N/128)*128][D padded to 32/64/128];
+ *   1  none (two-kernel deterministic mode: dQ is recomputed from S and dP);
+ *   2  the dS scratch of the spill mode, 32 KiB per (KV tile, Q tile) pair of one chunk.
+ */
 size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic);
+
+/*
+ * Upper bound of the spill-mode scratch in bytes (default 8 GiB); returns the previous value.
+ * Larger problems run in chunks of batch entries / head ranges that fit, one after the other.
+ * The split is a function of (H, N) and this bound only and never changes a bit of the
+ * results.  Process-wide; do not change it while calls are in flight on other threads, and
+ * query fa2_bwd_workspace_bytes again after changing it.  No counterpart in the reference.
+ */
+size_t fa2_set_spill_budget(size_t bytes);
 
 /*
  * The same three operations on tensors that are not dense: any batch, head and row strides

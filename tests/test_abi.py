@@ -135,3 +135,35 @@ def test_key_count_must_not_exceed_query_count():
                                0.125, None, None) == -5
     assert lib.fa2_fwd_strided(0x1000, 0x2000, 0x3000, 0x4000, 0x5000, 1, 1, 128, 0, 64, 0,
                                0.125, None, None) == -5
+
+
+def test_spill_scratch_size_follows_the_budget():
+    """32 KiB per (KV tile, Q tile) pair, bounded by fa2_set_spill_budget through chunking."""
+    lib = _lib.lib()
+    pairs = 64 * 65 // 2  # N = 8192: 64 tiles
+    previous = lib.fa2_set_spill_budget(1 << 40)
+    try:
+        assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == 2 * 32 * pairs * 32768
+        lib.fa2_set_spill_budget(40 * pairs * 32768)      # one batch entry (32 heads) fits, two do not
+        assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == 32 * pairs * 32768
+        lib.fa2_set_spill_budget(20 * pairs * 32768)      # 20 heads fit: two chunks of 16
+        assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == 16 * pairs * 32768
+        lib.fa2_set_spill_budget(1)                       # never below one head
+        assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == pairs * 32768
+        assert lib.fa2_set_spill_budget(previous) == 1
+    finally:
+        lib.fa2_set_spill_budget(previous)
+    assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 1) == 0
+
+
+def test_backward_mode_choice_depends_on_the_sequence_length_only(monkeypatch):
+    from flash_attention_triton_b200 import api
+
+    monkeypatch.delenv("FA2_B200_BWD_MODE", raising=False)
+    assert api._backward_mode(True, 128, 8192) == api._MODE_SPILL
+    assert api._backward_mode(True, 32, 4095) == api._MODE_SPILL
+    assert api._backward_mode(True, 128, 65536) == api._MODE_RECOMPUTE   # 4 GiB of dS per head
+    assert api._backward_mode(False, 128, 8192) == api._MODE_SPILL       # fastest at d = 128
+    assert api._backward_mode(False, 64, 8192) == api._MODE_ATOMIC
+    monkeypatch.setenv("FA2_B200_BWD_MODE", "recompute")
+    assert api._backward_mode(False, 64, 8192) == api._MODE_RECOMPUTE

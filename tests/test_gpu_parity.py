@@ -81,14 +81,41 @@ CASES = [
 ]
 
 
-@pytest.mark.parametrize("det", [True, False], ids=["det", "atomic"])
+@pytest.mark.parametrize("mode", ["spill", "recompute", "atomic"])
 @pytest.mark.parametrize("shape,dtype,scale,qk_mul", CASES,
                          ids=[f"{'x'.join(map(str, c[0]))}-{str(c[1])[6:]}" for c in CASES])
-def test_forward_backward_match_oracle(shape, dtype, scale, qk_mul, det):
+def test_forward_backward_match_oracle(shape, dtype, scale, qk_mul, mode, monkeypatch):
+    """Every dQ strategy of the backward (the API picks one per shape; here each is forced)."""
+    monkeypatch.setenv("FA2_B200_BWD_MODE", mode)
     q, k, v, do = make_inputs(shape, dtype, seed=0, qk_mul=qk_mul)
     ref = naive_attention(q, k, v, do, scale)
-    got = run_api(q, k, v, do, scale, det)
+    got = run_api(q, k, v, do, scale, mode != "atomic")
     check_against(ref, got, dtype)
+
+
+def test_spill_mode_chunks_change_no_bit(monkeypatch):
+    """With a scratch bound of 3 MiB the spill mode works through [3, 5, 700, 64] (0.7 MiB per
+    head) in chunks of 3 + 2 heads per batch entry; with 8 MiB in chunks of 2 + 1 batch
+    entries; unbounded in one piece.  Same bits every time, and dK, dV equal the recompute
+    mode's."""
+    monkeypatch.setenv("FA2_B200_BWD_MODE", "spill")
+    q, k, v, do = make_inputs((3, 5, 700, 64), torch.float16, seed=4)
+    lib = _lib.lib()
+    previous = lib.fa2_set_spill_budget(1 << 40)
+    try:
+        whole = run_api(q, k, v, do, None, True)
+        for budget in (3 << 20, 8 << 20, 1):
+            lib.fa2_set_spill_budget(budget)
+            assert lib.fa2_bwd_workspace_bytes(3, 5, 700, 64, 2) <= max(budget, 21 * 32768)
+            chunked = run_api(q, k, v, do, None, True)
+            for key in whole:
+                assert torch.equal(chunked[key], whole[key]), (key, budget)
+    finally:
+        lib.fa2_set_spill_budget(previous)
+    monkeypatch.setenv("FA2_B200_BWD_MODE", "recompute")
+    recompute = run_api(q, k, v, do, None, True)
+    assert torch.equal(recompute["dk"], whole["dk"]) and torch.equal(recompute["dv"], whole["dv"])
+    assert (recompute["dq"].float() - whole["dq"].float()).abs().max() <= 2e-3
 
 
 def test_lse_and_rowstats_through_the_c_abi():
@@ -197,7 +224,7 @@ def test_unsupported_head_dim_raises():
         flash_attention_v2(q, q, q)
 
 
-@pytest.mark.parametrize("det", [True, False], ids=["det", "atomic"])
+@pytest.mark.parametrize("mode", ["spill", "recompute", "atomic"])
 @pytest.mark.parametrize(
     "nq,nk,d,dtype",
     [
@@ -208,9 +235,11 @@ def test_unsupported_head_dim_raises():
         (129, 1, 64, torch.float16),      # a single key
     ],
 )
-def test_seqlen_q_differs_from_seqlen_k(nq, nk, d, dtype, det):
+def test_seqlen_q_differs_from_seqlen_k(nq, nk, d, dtype, mode, monkeypatch):
     """Top-left aligned causal mask as in the reference (_triton_kernels_v2.py:139-147):
     query row i sees keys 0 .. min(i, seqlen_k - 1)."""
+    monkeypatch.setenv("FA2_B200_BWD_MODE", mode)
+    det = mode != "atomic"
     g = torch.Generator().manual_seed(nq + nk)
     q, do = (torch.randn(2, 2, nq, d, generator=g).to(dtype) for _ in range(2))
     k, v = (torch.randn(2, 2, nk, d, generator=g).to(dtype) for _ in range(2))
