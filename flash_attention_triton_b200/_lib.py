@@ -27,6 +27,7 @@ SYMBOLS = [
     ("fa2_set_spill_budget", c_size_t, [c_size_t]),
     ("fa2_device_status", c_int, [ctypes.POINTER(c_int)]),
     ("fa2_selftest_mma", c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    ("fa2_selftest_wait_timeout", c_int, [c_void_p]),
     ("fa2_bwd_static_scratch", c_int, [c_void_p] * 9 + [c_int] * 5 + [c_float, c_void_p]),
     ("fa2_fwd_strided", c_int, [c_void_p] * 5 + [c_int] * 6 + [c_float, c_void_p, c_void_p]),
     ("fa2_bwd_preprocess_strided", c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p, c_void_p]),

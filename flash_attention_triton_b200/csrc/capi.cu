@@ -383,6 +383,12 @@ int fa2_device_status(int* status_out) {
   return static_cast<int>(ce);
 }
 
+int fa2_selftest_wait_timeout(fa2_stream_t stream) {
+  DeviceState* d = nullptr;
+  if (int e = device_state(&d)) return e;
+  return static_cast<int>(launch_selftest_wait(d->status, static_cast<cudaStream_t>(stream)));
+}
+
 int fa2_selftest_mma(int form, const void* a, const void* b, float* c, int D, int dtype,
                      fa2_stream_t stream) {
   if (!a || !b || !c) return FA2_ERR_NULL_POINTER;

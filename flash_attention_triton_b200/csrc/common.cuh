@@ -126,6 +126,10 @@ cudaError_t launch_bwd_dq(const AttnShape& s, const CUtensorMap& tq, const CUten
 cudaError_t launch_dq_convert(const AttnShape& s, const float* dq_accum, void* dq,
                               const Strides& sdq, cudaStream_t stream);
 
+// One CTA whose waits run into the time limit on purpose (nothing ever arrives); it must end
+// by itself with the status word set.
+cudaError_t launch_selftest_wait(int* status, cudaStream_t stream);
+
 cudaError_t launch_selftest_mma(int form, const CUtensorMap& ta, const CUtensorMap& tb,
                                 const void* a_raw, float* c, int D, int dtype, int* status,
                                 cudaStream_t stream);

@@ -151,6 +151,26 @@ __global__ void __launch_bounds__(kSelfThreads, 1)
   }
 }
 
+// Bounded-wait self-test: two warps wait on an mbarrier that nobody arrives at.  The first
+// waiter to reach the time limit sets the CTA's abort flag and the device status word; the
+// other one sees the flag and leaves; the kernel ends normally and the context stays usable.
+constexpr int kSiteWaitProbe = 120;
+__global__ void __launch_bounds__(64, 1) wait_probe_kernel(int* status) {
+  __shared__ __align__(8) uint64_t bar_storage;
+  __shared__ int abort_storage;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    abort_storage = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const WaitCtx w{&abort_storage, status};
+  const bool ok = mbar_wait_warp(bar, 0, w, kSiteWaitProbe);  // never completes: returns false
+  if (ok && threadIdx.x == 0) atomicCAS(status, 0, 0x30000 | kSiteWaitProbe);  // must not happen
+  __syncthreads();
+}
+
 template <int D, bool BF16>
 cudaError_t launch_t(int form, const CUtensorMap& ta, const CUtensorMap& tb, const void* a_raw,
                      float* c, int* status, cudaStream_t stream) {
@@ -180,6 +200,11 @@ cudaError_t launch_selftest_mma(int form, const CUtensorMap& ta, const CUtensorM
   }
 #undef FA2_CASE
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_selftest_wait(int* status, cudaStream_t stream) {
+  wait_probe_kernel<<<1, 64, 0, stream>>>(status);
+  return cudaGetLastError();
 }
 
 }  // namespace fa2

@@ -182,6 +182,15 @@ int fa2_device_status(int* status_out);
  *   form 2: C[128,D]   = A[128,128]^T * B[128,D]    (A staged transposed in shared memory)
  * a, b: 16-bit inputs of `dtype`; c: fp32 output.  No counterpart in the reference.
  */
+/*
+ * Diagnostics: launches one small CTA whose threads wait for a barrier that nobody arrives at.
+ * The wait is bounded like every wait in this library: after about two seconds the kernel sets
+ * the status word (fa2_device_status then reports 0x10000 | 120), its other waiters leave, and it
+ * ends normally; the context stays usable.  Shows that a lost signal cannot hang the GPU.
+ * No counterpart in the reference.
+ */
+int fa2_selftest_wait_timeout(fa2_stream_t stream);
+
 int fa2_selftest_mma(int form, const void* a, const void* b, float* c,
                      int D, int dtype, fa2_stream_t stream);
 

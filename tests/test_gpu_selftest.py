@@ -30,3 +30,20 @@ def test_mma_operand_forms(form, d, dtype):
     assert _lib.device_status() == 0
     # fp32 accumulation of exact 16-bit products: error is a few fp32 ulps of the result
     assert (c.cpu().double() - ref).abs().max().item() < 1e-3
+
+
+def test_a_lost_signal_ends_in_a_status_word_not_in_a_hang():
+    """Two warps wait for a barrier nobody arrives at; the bounded wait gives up after about two
+    seconds, the kernel ends by itself, fa2_device_status reports where, and the next kernel runs
+    as if nothing had happened."""
+    lib = _lib.lib()
+    assert _lib.device_status() == 0
+    assert lib.fa2_selftest_wait_timeout(torch.cuda.current_stream().cuda_stream) == 0
+    assert _lib.device_status() == (0x10000 | 120)
+    assert _lib.device_status() == 0  # reading clears it
+    q = torch.randn(1, 1, 128, 64, device="cuda", dtype=torch.float16)
+    from flash_attention_triton_b200 import flash_attention_v2
+
+    out = flash_attention_v2(q, q, q)
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all() and _lib.device_status() == 0
