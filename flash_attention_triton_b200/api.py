@@ -32,7 +32,8 @@ import torch
 
 from . import _lib
 
-_MAX_HEAD_DIM = 128
+_MAX_HEAD_DIM = 256           # forward (the reference's max_headdim on B200, line 533)
+_MAX_HEAD_DIM_BACKWARD = 128  # the backward kernels stop here
 
 
 # ------------------------------------------------------------------ host launch wrappers
@@ -226,6 +227,11 @@ class FlashAttentionV2Function(torch.autograd.Function):
         pad = q.shape[-1] - ctx.headdim
         if pad:
             d_output = torch.nn.functional.pad(d_output, (0, pad))
+        if q.shape[-1] > _MAX_HEAD_DIM_BACKWARD:
+            raise ValueError(
+                f"head dimension {ctx.headdim}: the backward supports at most {_MAX_HEAD_DIM_BACKWARD} "
+                f"(the forward goes up to {_MAX_HEAD_DIM})"
+            )
         _flash_attention_backward(
             q, k, v, output, lse, dq, dk, dv, d_output, ctx.softmax_scale, ctx.deterministic,
         )

@@ -146,7 +146,7 @@ void make_ctx(DeviceState* d, LaunchCtx* ctx) {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int check_shape(int B, int H, int N, int D, int dtype) {
-  if (D < 8 || D > 128 || D % 8 != 0) return FA2_ERR_HEAD_DIM;
+  if (D < 8 || D > 256 || D % 8 != 0) return FA2_ERR_HEAD_DIM;
   if (dtype != FA2_DTYPE_FP16 && dtype != FA2_DTYPE_BF16) return FA2_ERR_DTYPE;
   if (B <= 0 || H <= 0 || N <= 0) return FA2_ERR_SHAPE;
   if (static_cast<long long>(B) * H > 65535) return FA2_ERR_SHAPE;
@@ -188,7 +188,7 @@ const char* fa2_strerror(int code) {
   switch (code) {
     case FA2_OK: return "success";
     case FA2_ERR_NULL_POINTER: return "a required pointer is NULL";
-    case FA2_ERR_HEAD_DIM: return "head dimension must be a multiple of 8 between 8 and 128";
+    case FA2_ERR_HEAD_DIM: return "head dimension must be a multiple of 8 between 8 and 256";
     case FA2_ERR_DTYPE: return "dtype must be 0 (fp16) or 1 (bf16)";
     case FA2_ERR_MISALIGNED: return "tensor pointers must be 16-byte aligned";
     case FA2_ERR_SHAPE: return "B, H, N must be positive, B*H <= 65535, N <= 2^24, 1 <= Nk <= N";
@@ -248,6 +248,7 @@ int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse
                                fa2_stream_t stream) {
   if (!o || !dout || !lse || !rowstats) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
+  if (D > 128) return FA2_ERR_HEAD_DIM;  // the backward stops at 128
   if (!aligned16(o) || !aligned16(dout) || !aligned16(rowstats)) return FA2_ERR_MISALIGNED;
   Strides so, sdo;
   if (int e = get_strides(strides, 0, B, H, N, D, &so)) return e;
@@ -280,6 +281,7 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
                     const long long* strides, fa2_stream_t stream) {
   if (!q || !k || !v || !dout || !rowstats || !dq || !dk || !dv) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
+  if (D > 128) return FA2_ERR_HEAD_DIM;  // the backward stops at 128
   if (Nk < 1 || Nk > N) return FA2_ERR_SHAPE;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(dout) || !aligned16(dq) ||
       !aligned16(dk) || !aligned16(dv) || !aligned16(rowstats))

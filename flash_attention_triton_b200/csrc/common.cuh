@@ -48,7 +48,7 @@ __host__ __device__ __forceinline__ uint32_t swizzled_offset_128B(uint32_t row, 
 struct AttnShape {
   int B, H;
   int N;      // query rows (rows of q, o, dout, dq, lse)
-  int D;      // head dim the kernels are instantiated for: 32, 64 or 128
+  int D;      // head dim the kernels are instantiated for: 32, 64, 128 or 256
   int dtype;  // 0 = fp16, 1 = bf16
   float scale;
   int Dg;     // head dim of the tensors in memory (a multiple of 8, <= D); the columns
@@ -63,7 +63,7 @@ struct Strides {
 };
 
 // Smallest instantiated head dim that holds `d` columns.
-inline int padded_head_dim(int d) { return d <= 32 ? 32 : (d <= 64 ? 64 : 128); }
+inline int padded_head_dim(int d) { return d <= 32 ? 32 : (d <= 64 ? 64 : (d <= 128 ? 128 : 256)); }
 
 // Per-launch context of the forward kernel.  It runs one CTA per SM; each CTA fetches work
 // items (pairs of Q tiles) from `work_counter` until none are left, so tensor memory is

@@ -87,8 +87,15 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap to,
                float* __restrict__ lse, int N, int Nk, int num_bh, int num_heads,
                float scale_log2, int* status, unsigned int* work_counter) {
-  using C = FwdCfg<D>;
-  using T = Tile<D>;
+  // Head dim 256 ("wide") runs on the staging and tensor-memory plan of head dim 128 with ONE
+  // Q tile per work item: the two Q slots hold the two 128-column halves of that tile, K and V
+  // tiles stream through their rings as half tiles, S = Q_lo K_lo^T + Q_hi K_hi^T accumulates
+  // over two products and O_lo / O_hi take the places of O0 / O1.  Only softmax group 0 works.
+  constexpr bool WIDE = D == 256;
+  constexpr int DT = WIDE ? 128 : D;    // columns of one staged tile
+  constexpr int HALVES = WIDE ? 2 : 1;  // staged tiles per 128 rows
+  using C = FwdCfg<DT>;
+  using T = Tile<DT>;
   extern __shared__ __align__(1024) uint8_t smem[];
 
   // Role index: hardware warps 0-3 take roles 8-11 (MMA, TMA, idle, idle) and hardware warps
@@ -110,7 +117,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
 
   const int ntiles = (N + 127) >> 7;
   const int nktiles = (Nk + 127) >> 7;
-  const int npairs = (ntiles + 1) >> 1;
+  const int npairs = WIDE ? ntiles : (ntiles + 1) >> 1;  // work items per (batch, head)
   const int total_items = npairs * num_bh;
 
   if (threadIdx.x == 0) *abort_flag = 0;
@@ -163,8 +170,8 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const int bh = item / npairs;
     const HeadCoord hc{bh % num_heads, bh / num_heads};
     const int pair = npairs - 1 - (item - bh * npairs);  // heavy pairs of a head first
-    const int qt0 = 2 * pair, qt1 = 2 * pair + 1;
-    const bool has1 = qt1 < ntiles;
+    const int qt0 = WIDE ? pair : 2 * pair, qt1 = qt0 + 1;
+    const bool has1 = !WIDE && qt1 < ntiles;
     // KV tiles of Q tile i: 0 .. min(i, last KV tile)  (N = query rows, Nk <= N = key rows)
     const int n0 = qt0 + 1 < nktiles ? qt0 + 1 : nktiles;
     const int n1 = has1 ? (qt1 + 1 < nktiles ? qt1 + 1 : nktiles) : 0;
@@ -182,35 +189,41 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         prefetch_tensormap(&tq);
         prefetch_tensormap(&tk);
         prefetch_tensormap(&tv);
-        mbar_arrive_expect_tx(bar(C::kBarQFull), (has1 ? 2 : 1) * T::kTileBytes);
-        for (int i = 0; i < (has1 ? 2 : 1); ++i)
+        const int nslots = (WIDE || has1) ? 2 : 1;
+        mbar_arrive_expect_tx(bar(C::kBarQFull), nslots * T::kTileBytes);
+        for (int i = 0; i < nslots; ++i)
           for (int ch = 0; ch < T::kChunks; ++ch)
             tma_load_4d(smem_base + C::kOffQ + i * T::kTileBytes + ch * T::kChunkTileBytes, &tq,
-                        ch * T::kChunkElems, (qt0 + i) * 128, hc, bar(C::kBarQFull));
+                        (WIDE ? i * 128 : 0) + ch * T::kChunkElems, (WIDE ? qt0 : qt0 + i) * 128, hc,
+                        bar(C::kBarQFull));
       }
-      // K runs one tile ahead of V: S(j+1) is issued during KV step j.
-      for (int j = 0; j <= nkv; ++j) {
-        if (j < nkv) {
-          const int ks = j % C::kKStages, kph = (j / C::kKStages) & 1;
+      // K runs one KV tile ahead of V: S(j+1) is issued during KV step j.  Ring entries are
+      // staged tiles: entry t holds columns (t % HALVES) * 128 .. of KV tile t / HALVES.
+      const int nsub = nkv * HALVES;
+      for (int t = 0; t < nsub + HALVES; ++t) {
+        if (t < nsub) {
+          const int ks = t % C::kKStages, kph = (t / C::kKStages) & 1;
           if (!mbar_wait_warp(bar(C::kBarKEmpty + ks), kph ^ 1, w, kSiteLoadK)) break;
           if (elected) {
             mbar_arrive_expect_tx(bar(C::kBarKFull + ks), T::kTileBytes);
 #pragma unroll
             for (int ch = 0; ch < T::kChunks; ++ch)
               tma_load_4d(smem_base + C::kOffK + ks * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
-                          ch * T::kChunkElems, j * 128, hc, bar(C::kBarKFull + ks));
+                          (t % HALVES) * 128 + ch * T::kChunkElems, (t / HALVES) * 128, hc,
+                          bar(C::kBarKFull + ks));
           }
         }
-        if (j > 0) {
-          const int jv = j - 1;
-          const int vs = jv % C::kVStages, vph = (jv / C::kVStages) & 1;
+        if (t >= HALVES) {
+          const int tv_ = t - HALVES;
+          const int vs = tv_ % C::kVStages, vph = (tv_ / C::kVStages) & 1;
           if (!mbar_wait_warp(bar(C::kBarVEmpty + vs), vph ^ 1, w, kSiteLoadV)) break;
           if (elected) {
             mbar_arrive_expect_tx(bar(C::kBarVFull + vs), T::kTileBytes);
 #pragma unroll
             for (int ch = 0; ch < T::kChunks; ++ch)
               tma_load_4d(smem_base + C::kOffV + vs * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
-                          ch * T::kChunkElems, jv * 128, hc, bar(C::kBarVFull + vs));
+                          (tv_ % HALVES) * 128 + ch * T::kChunkElems, (tv_ / HALVES) * 128, hc,
+                          bar(C::kBarVFull + vs));
           }
         }
       }
@@ -226,8 +239,16 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       bool ok = mbar_wait(bar(C::kBarQFull), 0, w, kSiteMmaQ);
       int ks = 0, kph = 0;          // K ring position of tile j
       int prev_i = -1, prev_ph = 0;  // group and phase of the previous score product
+      auto next_k = [&]() {
+        if (++ks == C::kKStages) {
+          ks = 0;
+          kph ^= 1;
+        }
+      };
       for (int j = 0; ok && j < nkv; ++j) {
-        if (!(ok = mbar_wait(bar(C::kBarKFull + ks), kph, w, kSiteMmaK))) break;
+        if constexpr (!WIDE) {
+          if (!(ok = mbar_wait(bar(C::kBarKFull + ks), kph, w, kSiteMmaK))) break;
+        }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           if (j >= (i == 0 ? n0 : n1)) continue;
@@ -236,19 +257,31 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
             tc_fence_after();
           }
           FA2_TRACE_EVENT(traced && elected, j * 16 + 4 + i);
-          issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColS,
-                                     smem_base + C::kOffQ + i * T::kTileBytes,
-                                     smem_base + C::kOffK + ks * T::kTileBytes);
+          if constexpr (WIDE) {
+            // S = Q_lo K_lo^T + Q_hi K_hi^T: the Q slots hold the halves, K arrives half by half
+            for (int half = 0; ok && half < 2; ++half) {
+              if (!(ok = mbar_wait(bar(C::kBarKFull + ks), kph, w, kSiteMmaK))) break;
+              issue_rows_x_rows<DT, BF16>(elected, tmem_base + C::kColS,
+                                          smem_base + C::kOffQ + half * T::kTileBytes,
+                                          smem_base + C::kOffK + ks * T::kTileBytes, half);
+              if (elected) mma_commit(bar(C::kBarKEmpty + ks));
+              next_k();
+            }
+            if (!ok) break;
+          } else {
+            issue_rows_x_rows<DT, BF16>(elected, tmem_base + C::kColS,
+                                        smem_base + C::kOffQ + i * T::kTileBytes,
+                                        smem_base + C::kOffK + ks * T::kTileBytes);
+          }
           if (elected) mma_commit(bar(C::kBarSFull + i));
           FA2_TRACE_EVENT(traced && elected, j * 16 + 0 + 2 * i);
           prev_i = i;
           prev_ph = j & 1;
         }
         if (!ok) break;
-        if (elected) mma_commit(bar(C::kBarKEmpty + ks));  // both products that read K_j issued
-        if (++ks == C::kKStages) {
-          ks = 0;
-          kph ^= 1;
+        if constexpr (!WIDE) {
+          if (elected) mma_commit(bar(C::kBarKEmpty + ks));  // both products that read K_j issued
+          next_k();
         }
       }
     } else if (warp == 10) {
@@ -256,25 +289,45 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       const uint32_t elected = elect_one();
       bool ok = true;
       int vs = 0, vph = 0;  // V ring position of tile j
+      auto next_v = [&]() {
+        if (++vs == C::kVStages) {
+          vs = 0;
+          vph ^= 1;
+        }
+      };
       for (int j = 0; ok && j < nkv; ++j) {
-        if (!(ok = mbar_wait(bar(C::kBarVFull + vs), vph, w, kSiteMmaV))) break;
+        if constexpr (!WIDE) {
+          if (!(ok = mbar_wait(bar(C::kBarVFull + vs), vph, w, kSiteMmaV))) break;
+        }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           if (j >= (i == 0 ? n0 : n1)) continue;
           if (!(ok = mbar_wait(bar(C::kBarPFull + i), j & 1, w, kSiteMmaP))) break;
           tc_fence_after();
           FA2_TRACE_EVENT(traced && elected, j * 16 + 6 + i);
-          issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColO + i * D,
-                                     tmem_base + C::kColP + i * 64, 32,
-                                     smem_base + C::kOffV + vs * T::kTileBytes, j > 0);
+          if constexpr (WIDE) {
+            // O_lo += P V_lo, O_hi += P V_hi: the O0 / O1 columns hold the two halves of O
+            for (int half = 0; ok && half < 2; ++half) {
+              if (!(ok = mbar_wait(bar(C::kBarVFull + vs), vph, w, kSiteMmaV))) break;
+              issue_tmem_x_tile<DT, BF16>(elected, tmem_base + C::kColO + half * DT,
+                                          tmem_base + C::kColP, 32,
+                                          smem_base + C::kOffV + vs * T::kTileBytes, j > 0);
+              if (elected) mma_commit(bar(C::kBarVEmpty + vs));
+              next_v();
+            }
+            if (!ok) break;
+          } else {
+            issue_tmem_x_tile<DT, BF16>(elected, tmem_base + C::kColO + i * DT,
+                                        tmem_base + C::kColP + i * 64, 32,
+                                        smem_base + C::kOffV + vs * T::kTileBytes, j > 0);
+          }
           if (elected) mma_commit(bar(C::kBarPvDone + i));
           FA2_TRACE_EVENT(traced && elected, j * 16 + 1 + 2 * i);
         }
         if (!ok) break;
-        if (elected) mma_commit(bar(C::kBarVEmpty + vs));
-        if (++vs == C::kVStages) {
-          vs = 0;
-          vph ^= 1;
+        if constexpr (!WIDE) {
+          if (elected) mma_commit(bar(C::kBarVEmpty + vs));
+          next_v();
         }
       }
     }
@@ -289,7 +342,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tS = tmem_base + lane_base + C::kColS;
     const uint32_t tP = tmem_base + lane_base + C::kColP + wg * 64;
-    const uint32_t tO = tmem_base + lane_base + C::kColO + wg * D;
+    const uint32_t tO = tmem_base + lane_base + C::kColO + wg * DT;  // wide: 256 columns, wg 0 only
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < nj; ++j) {
@@ -404,7 +457,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
           val.w = pack2<BF16>(__uint_as_float(orr[8 * p + 6]) * inv_l,
                               __uint_as_float(orr[8 * p + 7]) * inv_l);
           *reinterpret_cast<uint4*>(sO + chunk * T::kChunkTileBytes +
-                                    swizzled_offset<D>(r, piece0 + p)) = val;
+                                    swizzled_offset<DT>(r, piece0 + p)) = val;
         }
       }
       fence_proxy_async_smem();
@@ -412,7 +465,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       if (lane == 0) {
         const int row0 = (warp & 3) * 32;
         if (qt * 128 + row0 < N) {
-          for (int ch = 0; ch < T::kChunks; ++ch)
+          for (int ch = 0; ch < D / T::kChunkElems; ++ch)
             tma_store_4d(&to, ch * T::kChunkElems, qt * 128 + row0, hc,
                          smem_u32(sO + ch * T::kChunkTileBytes + row0 * T::kRowBytes));
           tma_store_commit();
@@ -440,13 +493,13 @@ template <int D, bool BF16>
 cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                          const CUtensorMap& tv, const CUtensorMap& to, float* lse,
                          const LaunchCtx& ctx, cudaStream_t stream) {
-  using C = FwdCfg<D>;
+  using C = FwdCfg<D == 256 ? 128 : D>;  // head dim 256 runs on the plan of head dim 128
   auto kern = fwd_kernel<D, BF16>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
   const int ntiles = (s.N + 127) / 128;
-  const int npairs = (ntiles + 1) / 2;
+  const int npairs = D == 256 ? ntiles : (ntiles + 1) / 2;
   const long long items = static_cast<long long>(npairs) * s.B * s.H;
   const unsigned grid = static_cast<unsigned>(items < ctx.num_sms ? items : ctx.num_sms);
   const float scale_log2 = s.scale * 1.4426950408889634f;
@@ -474,6 +527,7 @@ cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensor
     FA2_CASE(32)
     FA2_CASE(64)
     FA2_CASE(128)
+    FA2_CASE(256)
   }
 #undef FA2_CASE
   return cudaErrorInvalidValue;

@@ -25,11 +25,12 @@ __device__ __forceinline__ uint32_t desc_lo_word(uint32_t saddr, uint32_t lbo_by
   return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
 }
 
-// acc[128, 128] = A[128 rows, D] * B[128 rows, D]^T.  Both tiles are K-major (row = M / N
+// acc[128, 128] (+)= A[128 rows, D] * B[128 rows, D]^T.  Both tiles are K-major (row = M / N
 // index, the contiguous dimension is the reduction index d), as TMA stages a [128, D] tile.
 template <int D, bool BF16>
 __device__ __forceinline__ void issue_rows_x_rows(uint32_t elected, uint32_t d_tmem,
-                                                  uint32_t a_addr, uint32_t b_addr) {
+                                                  uint32_t a_addr, uint32_t b_addr,
+                                                  uint32_t accumulate = 0u) {
   using T = Tile<D>;
   constexpr uint32_t idesc = make_idesc(128, 128, BF16, false, false);
   constexpr uint32_t hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
@@ -40,7 +41,7 @@ __device__ __forceinline__ void issue_rows_x_rows(uint32_t elected, uint32_t d_t
     const uint32_t off16 = ((k / kpc) * T::kChunkTileBytes + (k % kpc) * 32) >> 4;
     if (elected)
       mma_ss(d_tmem, desc_from_words(a_lo + off16, hi), desc_from_words(b_lo + off16, hi), idesc,
-             k > 0 ? 1u : 0u);
+             k > 0 ? 1u : accumulate);
   }
 }
 

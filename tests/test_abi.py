@@ -62,7 +62,7 @@ def test_size_queries():
     [
         (dict(q=0), -1),                      # NULL pointer
         (dict(D=44), -2),                     # head dim not a multiple of 8
-        (dict(D=136), -2),                    # head dim above 128
+        (dict(D=264), -2),                    # head dim above 256
         (dict(dtype=7), -3),                  # unsupported dtype
         (dict(q=0x1008), -4),                 # misaligned pointer
         (dict(N=0), -5),                      # empty sequence

@@ -219,9 +219,47 @@ def test_packed_qkv_through_the_strided_c_abi(det):
 
 
 def test_unsupported_head_dim_raises():
-    q = torch.randn(1, 1, 64, 160, device=DEV, dtype=torch.float16)
+    q = torch.randn(1, 1, 64, 264, device=DEV, dtype=torch.float16)
     with pytest.raises(ValueError, match="head dimension"):
         flash_attention_v2(q, q, q)
+    q = torch.randn(1, 1, 64, 160, device=DEV, dtype=torch.float16, requires_grad=True)
+    out = flash_attention_v2(q, q, q)  # the forward goes up to 256 ...
+    with pytest.raises(ValueError, match="backward supports at most 128"):
+        out.sum().backward()           # ... the backward stops at 128
+
+
+@pytest.mark.parametrize(
+    "shape,dtype",
+    [
+        ((2, 2, 1000, 256), torch.bfloat16),  # the reference's max_headdim
+        ((1, 3, 300, 160), torch.float16),
+        ((1, 2, 129, 192), torch.bfloat16),
+        ((1, 2, 640, 136), torch.float16),
+    ],
+    ids=lambda v: "x".join(map(str, v)) if isinstance(v, tuple) else str(v)[6:],
+)
+def test_forward_with_head_dims_up_to_256(shape, dtype):
+    """Head dims in (128, 256] run the forward on the 128-wide plan with one Q tile per CTA and
+    the head dim split in two halves (zero-padded to 256 by TMA like every other in-between
+    size); O and LSE against the fp64 definition."""
+    q, k, v, _ = make_inputs(shape, dtype)
+    ref = naive_attention(q, k, v)
+    with torch.no_grad():
+        out = flash_attention_v2(q.to(DEV), k.to(DEV), v.to(DEV))
+    assert _lib.device_status() == 0
+    check_against(ref, {"o": out}, dtype, keys=("o",))
+    # LSE through the C ABI
+    b, h, n, d = shape
+    lib = _lib.lib()
+    qd, kd, vd = (t.to(DEV) for t in (q, k, v))
+    o = torch.empty_like(qd)
+    lse = torch.empty(b, h, n, device=DEV, dtype=torch.float32)
+    assert lib.fa2_fwd(qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                       b, h, n, d, 0 if dtype == torch.float16 else 1, 1.0 / math.sqrt(d),
+                       torch.cuda.current_stream().cuda_stream) == 0
+    assert _lib.device_status() == 0
+    assert torch.equal(o, out)
+    assert (lse.cpu().double() - ref["lse"]).abs().max() <= 2e-3
 
 
 @pytest.mark.parametrize("mode", ["spill", "recompute", "atomic"])
