@@ -12,10 +12,10 @@ Mirrors ``src/flash_attention_triton/flash_attention_2.py`` of flash-attention-t
 
 Differences, all deliberate: fp16 and bf16 inputs run natively (the reference casts
 everything to fp16, lines 316/379); other float dtypes are cast to fp16 exactly as the
-reference does.  Head dimensions up to 128 are supported (multiples of 8 natively: the
-kernels run them zero-padded to 32 / 64 / 128 through TMA out-of-bounds fill; other sizes are
-zero-padded to a multiple of 8 on the host first).  ``seqlen_q != seqlen_k`` follows the
-reference's top-left aligned causal mask: query row i sees keys ``0 .. min(i, seqlen_k - 1)``;
+reference does.  Multiples of 8 run natively as head dimension (the kernels run them
+zero-padded to 32 / 64 / 128 / 256 through TMA out-of-bounds fill; other sizes are
+zero-padded to a multiple of 8 on the host first); head dimensions up to 256 are supported.
+``seqlen_q != seqlen_k`` follows the reference's top-left aligned causal mask: query row i sees keys ``0 .. min(i, seqlen_k - 1)``;
 keys beyond ``seqlen_q`` are seen by nobody and get zero gradients.
 Everything runs through the C library on the tensors' CUDA device; there is no fallback.
 """
@@ -32,8 +32,7 @@ import torch
 
 from . import _lib
 
-_MAX_HEAD_DIM = 256           # forward (the reference's max_headdim on B200, line 533)
-_MAX_HEAD_DIM_BACKWARD = 128  # the backward kernels stop here
+_MAX_HEAD_DIM = 256  # the reference's max_headdim on B200 (line 533)
 
 
 # ------------------------------------------------------------------ host launch wrappers
@@ -118,6 +117,8 @@ def _backward_mode(deterministic: bool, headdim: int, seqlen_q: int) -> int:
     (head dims above 64), the atomic kernel elsewhere.  ``FA2_B200_BWD_MODE`` = ``atomic`` /
     ``recompute`` / ``spill`` overrides both (for experiments).
     """
+    if headdim > 128:  # one (deterministic) backward exists there: scores + three consumers
+        return _MODE_SPILL
     forced = os.environ.get("FA2_B200_BWD_MODE")
     if forced:
         return {"atomic": _MODE_ATOMIC, "recompute": _MODE_RECOMPUTE, "spill": _MODE_SPILL}[forced]
@@ -227,11 +228,6 @@ class FlashAttentionV2Function(torch.autograd.Function):
         pad = q.shape[-1] - ctx.headdim
         if pad:
             d_output = torch.nn.functional.pad(d_output, (0, pad))
-        if q.shape[-1] > _MAX_HEAD_DIM_BACKWARD:
-            raise ValueError(
-                f"head dimension {ctx.headdim}: the backward supports at most {_MAX_HEAD_DIM_BACKWARD} "
-                f"(the forward goes up to {_MAX_HEAD_DIM})"
-            )
         _flash_attention_backward(
             q, k, v, output, lse, dq, dk, dv, d_output, ctx.softmax_scale, ctx.deterministic,
         )

@@ -104,7 +104,7 @@ __host__ __device__ __forceinline__ int dstile_count(int ntiles, int jt) {
 // MODE 0: dK, dV only (dQ comes from bwd_dq_kernel).  MODE 1 (fused): also dQ, accumulated into
 // an fp32 buffer with atomic adds by a fourth warp group.  MODE 2 (spill): also stores every
 // 16-bit dS^T tile to a scratch tensor (dq_accum then points to it), from which
-// bwd_dq_spill_kernel forms dQ with one product per tile pair instead of recomputing S, P, dP.
+// bwd_consume_kernel forms dQ with one product per tile pair instead of recomputing S, P, dP.
 template <int D, int MODE>
 struct DkdvCfg {
   using T = Tile<D>;
@@ -847,21 +847,26 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
 }
 
 // =========================================================================================
-// dQ from spilled dS tiles (spill mode).  CTA = one Q tile; dQ = sum_j dS(j)^T-tile^T K_j in
-// ascending KV order, one tensor-core product per KV tile, no exponentials: the kernel is
-// bound by reading the 32 KiB dS tile per product from HBM.
-//   warps 0-3  epilogue (dQ: tensor memory -> 16 bit -> TMA store)
-//   warp  4    TMA producer: ring of kStages x (dS^T tile + K tile)
+// One output tile from spilled 16-bit tiles (spill mode).  A CTA owns one output tile and adds
+// one tensor-core product per tile pair in ascending order, no exponentials; the kernel is bound
+// by reading the 32 KiB scratch tile per product from HBM.
+//   FORM 2: dQ(qt) = sum_j dS(j, qt) K_j      A = dS^T tile transposed (MN-major pieces)
+//   FORM 0: dV(jt) = sum_i P(jt, i)^T dO_i    A = P^T tile as stored   (K-major pieces)
+//   FORM 1: dK(jt) = sum_i dS(jt, i)^T Q_i    A = dS^T tile as stored  (K-major pieces)
+// (forms 0 and 1 serve head dim 256, where dK and dV do not fit next to the scores in tensor
+// memory.)
+//   warps 0-3  epilogue (tensor memory -> 16 bit -> TMA store)
+//   warp  4    TMA producer: ring of kStages x (scratch tile + operand tile)
 //   warp  5    MMA issue
 // =========================================================================================
 template <int D>
-struct DqSpillCfg {
+struct ConsumeCfg {
   using T = Tile<D>;
-  static constexpr int kStages = D == 128 ? 3 : 4;
+  static constexpr int kStages = D == 256 ? 2 : (D == 128 ? 3 : 4);
   static constexpr int kThreads = 192;
   static constexpr int kLoadWarp = 4;
   static constexpr int kMmaWarp = 5;
-  static constexpr int kStageBytes = 32768 + T::kTileBytes;  // dS^T tile, then the K tile
+  static constexpr int kStageBytes = 32768 + T::kTileBytes;  // scratch tile, then the operand tile
   static constexpr int kOffBar = kStages * kStageBytes;
   static constexpr int kBarFull = 0;
   static constexpr int kBarEmpty = kStages;
@@ -872,12 +877,11 @@ struct DqSpillCfg {
   static_assert(kSmemBytes <= 232448, "shared memory budget of one CTA");
 };
 
-template <int D, bool BF16>
-__global__ void __launch_bounds__(DqSpillCfg<D>::kThreads, 1)
-    bwd_dq_spill_kernel(const uint4* __restrict__ ds_scratch,
-                        const __grid_constant__ CUtensorMap tk,
-                        const __grid_constant__ CUtensorMap tdq, int N, int Nk, int* status) {
-  using C = DqSpillCfg<D>;
+template <int D, bool BF16, int FORM>
+__global__ void __launch_bounds__(ConsumeCfg<D>::kThreads, 1)
+    bwd_consume_kernel(const uint4* __restrict__ scratch, const __grid_constant__ CUtensorMap tb,
+                       const __grid_constant__ CUtensorMap tout, int N, int Nk, int* status) {
+  using C = ConsumeCfg<D>;
   using T = Tile<D>;
   extern __shared__ __align__(1024) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -891,13 +895,16 @@ __global__ void __launch_bounds__(DqSpillCfg<D>::kThreads, 1)
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   auto bar = [&](int i) { return smem_base + C::kOffBar + 8u * i; };
 
-  const int ntiles = (N + 127) >> 7;
-  const int nktiles = (Nk + 127) >> 7;
-  const int qt = ntiles - 1 - static_cast<int>(blockIdx.x);  // heaviest Q tile first
+  const int ntiles = (N + 127) >> 7;     // Q tiles
+  const int nktiles = (Nk + 127) >> 7;   // KV tiles
   const HeadCoord hc{static_cast<int>(blockIdx.y), static_cast<int>(blockIdx.z)};  // grid (tiles, H, B)
   const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
-  const int nkv = qt + 1 < nktiles ? qt + 1 : nktiles;
   const int head_tile0 = bh * dstile_count(ntiles, nktiles);
+  // The output tile and the range of tiles it is summed over (heaviest output tile first).
+  const int ot = FORM == 2 ? ntiles - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
+  const int first = FORM == 2 ? 0 : ot;
+  const int count = FORM == 2 ? (ot + 1 < nktiles ? ot + 1 : nktiles) : ntiles - ot;
+  const int out_rows = FORM == 2 ? N : Nk;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < C::kStages; ++i) {
@@ -921,33 +928,38 @@ __global__ void __launch_bounds__(DqSpillCfg<D>::kThreads, 1)
 
   if (warp == C::kLoadWarp) {
     const uint32_t elected = elect_one();
-    if (elected) prefetch_tensormap(&tk);
-    for (int j = 0; j < nkv; ++j) {
-      const int st = j % C::kStages, ph = (j / C::kStages) & 1;
+    if (elected) prefetch_tensormap(&tb);
+    for (int n = 0; n < count; ++n) {
+      const int st = n % C::kStages, ph = (n / C::kStages) & 1;
       if (!mbar_wait_warp(bar(C::kBarEmpty + st), ph ^ 1, w, kBSiteLoadQ)) break;
       if (elected) {
         const uint32_t dst = smem_base + st * C::kStageBytes;
-        const int tile = head_tile0 + dstile_count(ntiles, j) + (qt - j);  // pair (KV j, Q qt)
+        const int other = first + n;  // the KV tile (form 2) or Q tile (forms 0, 1) of this product
+        // pair (KV tile, Q tile) -> scratch tile: pairs of a head are numbered KV tile by KV tile
+        const int tile = FORM == 2 ? head_tile0 + dstile_count(ntiles, other) + (ot - other)
+                                   : head_tile0 + dstile_count(ntiles, ot) + n;
         mbar_arrive_expect_tx(bar(C::kBarFull + st), C::kStageBytes);
-        bulk_load_1d(dst, ds_scratch + static_cast<size_t>(tile) * 2048, 32768,
+        bulk_load_1d(dst, scratch + static_cast<size_t>(tile) * 2048, 32768,
                      bar(C::kBarFull + st));  // a tile is 32 KiB, stored as it is used
 #pragma unroll
         for (int ch = 0; ch < T::kChunks; ++ch)
-          tma_load_4d(dst + 32768 + ch * T::kChunkTileBytes, &tk, ch * T::kChunkElems, j * 128, hc,
-                      bar(C::kBarFull + st));
+          tma_load_4d(dst + 32768 + ch * T::kChunkTileBytes, &tb, ch * T::kChunkElems, other * 128,
+                      hc, bar(C::kBarFull + st));
       }
     }
     __syncwarp();
   } else if (warp == C::kMmaWarp) {
     const uint32_t elected = elect_one();
     bool ok = true;
-    for (int j = 0; ok && j < nkv; ++j) {
-      const int st = j % C::kStages, ph = (j / C::kStages) & 1;
+    for (int n = 0; ok && n < count; ++n) {
+      const int st = n % C::kStages, ph = (n / C::kStages) & 1;
       if (!(ok = mbar_wait(bar(C::kBarFull + st), ph, w, kBSiteMmaKV))) break;
       const uint32_t src = smem_base + st * C::kStageBytes;
-      // dQ[128 q, D] += dS[q, kv] K[kv, d]: A = the dS^T tile (q contiguous, MN-major, piece-
-      // major unswizzled), B = the K tile (d contiguous, MN-major)
-      issue_piecesT_x_tile<D, BF16>(elected, tmem_base, src, src + 32768, j > 0);
+      // out[128, D] += A * B; B = the operand tile (d contiguous, MN-major)
+      if constexpr (FORM == 2)
+        issue_piecesT_x_tile<D, BF16>(elected, tmem_base, src, src + 32768, n > 0);
+      else
+        issue_pieces_x_tile<D, BF16>(elected, tmem_base, src, src + 32768, n > 0);
       if (elected) mma_commit(bar(C::kBarEmpty + st));
     }
     if (ok && elected) mma_commit(bar(C::kBarDone));
@@ -957,7 +969,8 @@ __global__ void __launch_bounds__(DqSpillCfg<D>::kThreads, 1)
       tc_fence_after();
       const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
       // every product has completed, so the ring is idle: stage through its first buffer
-      store_rows_16bit<D, BF16>(tmem_base + lane_base, smem, warp, lane, &tdq, qt * 128, hc, N);
+      store_rows_16bit<D, BF16>(tmem_base + lane_base, smem, warp, lane, &tout, ot * 128, hc,
+                                out_rows);
     }
   }
 
@@ -967,6 +980,296 @@ __global__ void __launch_bounds__(DqSpillCfg<D>::kThreads, 1)
     tc_fence_after();
     tmem_dealloc(tmem_base, C::kTmemCols);
   }
+}
+
+// =========================================================================================
+// Head dim 256: scores only.  dK and dV alone would fill the 512 tensor-memory columns, so the
+// backward is split: this kernel forms P^T and dS^T for every (KV tile, Q tile) pair and writes
+// both as 16-bit piece-major tiles to two scratch tensors; bwd_consume_kernel then forms dV, dK
+// and dQ from them.  CTA = one KV tile.  K and V stay in shared memory as two half tiles each
+// (128 KiB); Q and dO stream through a ring of three half-tile slots; St and dPt are double
+// buffered in tensor memory (4 x 128 columns) and accumulate over the two halves of the head dim.
+//   warps 0-7  compute (as in bwd_dkdv_kernel: kv row per thread, two groups of 64 q columns)
+//   warp  8    MMA issue: St(i) = K_lo Q_lo^T + K_hi Q_hi^T, dPt(i) = V_lo dO_lo^T + V_hi dO_hi^T
+//   warp  9    TMA producer
+// =========================================================================================
+struct ScoresCfg {
+  using T = Tile<128>;
+  static constexpr int kThreads = 384;
+  static constexpr int kMmaWarp = 8;
+  static constexpr int kLoadWarp = 9;
+  static constexpr int kRing = 3;
+  static constexpr int kOffK = 0;                                   // K_lo, K_hi
+  static constexpr int kOffV = 2 * T::kTileBytes;                   // V_lo, V_hi
+  static constexpr int kOffRing = 4 * T::kTileBytes;                // Q_lo, Q_hi, dO_lo, dO_hi stream
+  static constexpr int kOffStats = kOffRing + kRing * T::kTileBytes;  // [2][256] fp32
+  static constexpr int kOffBar = kOffStats + 2 * 1024;
+  static constexpr int kBarKV = 0;
+  static constexpr int kBarRingFull = 1;
+  static constexpr int kBarRingEmpty = kBarRingFull + kRing;
+  static constexpr int kBarStFull = kBarRingEmpty + kRing;  // 2
+  static constexpr int kBarStFree = kBarStFull + 2;         // 2, 8 arrivals
+  static constexpr int kBarDptFull = kBarStFree + 2;        // 2
+  static constexpr int kBarDptFree = kBarDptFull + 2;       // 2, 8 arrivals
+  static constexpr int kBarStatsFull = kBarDptFree + 2;     // 2
+  static constexpr int kBarStatsFree = kBarStatsFull + 2;   // 2, 8 arrivals
+  static constexpr int kNumBars = kBarStatsFree + 2;
+  static constexpr int kSmemBytes = kOffBar + kNumBars * 8 + 16;
+  static_assert(kSmemBytes <= 232448, "shared memory budget of one CTA");
+  static constexpr int kColSt = 0;     // 2 x 128
+  static constexpr int kColDpt = 256;  // 2 x 128
+  static constexpr int kTmemCols = 512;
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(ScoresCfg::kThreads, 1)
+    bwd_scores_wide_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
+                           const __grid_constant__ CUtensorMap tv,
+                           const __grid_constant__ CUtensorMap tdo, const float* __restrict__ rowstats,
+                           uint4* __restrict__ p_scratch, uint4* __restrict__ ds_scratch, int N, int Nk,
+                           float scale, float scale_log2, int* status) {
+  using C = ScoresCfg;
+  using T = Tile<128>;
+  extern __shared__ __align__(1024) uint8_t smem[];
+  constexpr int kWarps = C::kThreads / 32;
+  const int warp = ((threadIdx.x >> 5) + C::kMmaWarp) % kWarps, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  if (smem_base & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(status, 0, 0x20000 | kBSiteAlign);
+    return;
+  }
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kOffBar);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  auto bar = [&](int i) { return smem_base + C::kOffBar + 8u * i; };
+
+  const int ntiles = (N + 127) >> 7;
+  const int nktiles = (Nk + 127) >> 7;
+  const int jt = blockIdx.x;  // KV tile
+  const HeadCoord hc{static_cast<int>(blockIdx.y), static_cast<int>(blockIdx.z)};  // grid (tiles, H, B)
+  const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
+  const int nq = ntiles - jt;  // Q tiles jt .. ntiles-1
+  const bool kv_ragged = jt * 128 + 128 > Nk;
+  const int tile0 = bh * dstile_count(ntiles, nktiles) + dstile_count(ntiles, jt);
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(C::kBarKV), 1);
+    for (int i = 0; i < C::kRing; ++i) {
+      mbar_init(bar(C::kBarRingFull + i), 1);
+      mbar_init(bar(C::kBarRingEmpty + i), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar(C::kBarStFull + i), 1);
+      mbar_init(bar(C::kBarStFree + i), 8);
+      mbar_init(bar(C::kBarDptFull + i), 1);
+      mbar_init(bar(C::kBarDptFree + i), 8);
+      mbar_init(bar(C::kBarStatsFull + i), 1);
+      mbar_init(bar(C::kBarStatsFree + i), 8);
+    }
+    *abort_flag = 0;
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == C::kMmaWarp) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const WaitCtx w{abort_flag, status};
+
+  if (warp >= C::kMmaWarp) {
+    reg_dec<72>();
+    if (warp == C::kLoadWarp) {
+      const uint32_t elected = elect_one();
+      if (elected) {
+        prefetch_tensormap(&tq);
+        prefetch_tensormap(&tk);
+        prefetch_tensormap(&tv);
+        prefetch_tensormap(&tdo);
+        mbar_arrive_expect_tx(bar(C::kBarKV), 4 * T::kTileBytes);
+        for (int half = 0; half < 2; ++half)
+          for (int ch = 0; ch < T::kChunks; ++ch) {
+            tma_load_4d(smem_base + C::kOffK + half * T::kTileBytes + ch * T::kChunkTileBytes, &tk,
+                        half * 128 + ch * T::kChunkElems, jt * 128, hc, bar(C::kBarKV));
+            tma_load_4d(smem_base + C::kOffV + half * T::kTileBytes + ch * T::kChunkTileBytes, &tv,
+                        half * 128 + ch * T::kChunkElems, jt * 128, hc, bar(C::kBarKV));
+          }
+      }
+      bool ok = true;
+      for (int i = 0; ok && i < nq; ++i) {
+        const int qt = jt + i;
+        // rowstats of Q tile qt -> stats buffer i % 2, once the compute warps are done with
+        // tile i - 2
+        if (!(ok = mbar_wait_warp(bar(C::kBarStatsFree + (i & 1)), ((i >> 1) & 1) ^ 1, w, kBSiteLoadQ)))
+          break;
+        if (elected) {
+          mbar_arrive_expect_tx(bar(C::kBarStatsFull + (i & 1)), 1024);
+          bulk_load_1d(smem_base + C::kOffStats + (i & 1) * 1024,
+                       rowstats + (static_cast<size_t>(bh) * ntiles + qt) * 256, 1024,
+                       bar(C::kBarStatsFull + (i & 1)));
+        }
+        for (int sub = 0; sub < 4; ++sub) {  // Q_lo, Q_hi, dO_lo, dO_hi
+          const int t = 4 * i + sub, slot = t % C::kRing, ph = (t / C::kRing) & 1;
+          if (!(ok = mbar_wait_warp(bar(C::kBarRingEmpty + slot), ph ^ 1, w, kBSiteLoadDO))) break;
+          if (elected) {
+            mbar_arrive_expect_tx(bar(C::kBarRingFull + slot), T::kTileBytes);
+#pragma unroll
+            for (int ch = 0; ch < T::kChunks; ++ch)
+              tma_load_4d(smem_base + C::kOffRing + slot * T::kTileBytes + ch * T::kChunkTileBytes,
+                          sub < 2 ? &tq : &tdo, (sub & 1) * 128 + ch * T::kChunkElems, qt * 128, hc,
+                          bar(C::kBarRingFull + slot));
+          }
+        }
+      }
+    } else if (warp == C::kMmaWarp) {
+      const uint32_t elected = elect_one();
+      auto commit = [&](int b) {
+        if (elected) mma_commit(bar(b));
+      };
+      bool ok = mbar_wait(bar(C::kBarKV), 0, w, kBSiteMmaKV);
+      for (int i = 0; ok && i < nq; ++i) {
+        const int b = i & 1, u = i >> 1;  // tensor-memory buffer and its use count
+        for (int prod = 0; ok && prod < 2; ++prod) {  // 0: St(i), 1: dPt(i)
+          if (u > 0) {
+            // the compute warps have copied use u - 1 of this buffer into registers
+            if (!(ok = mbar_wait(bar((prod ? C::kBarDptFree : C::kBarStFree) + b), (u - 1) & 1, w,
+                                 kBSiteMmaDrain)))
+              break;
+            tc_fence_after();
+          }
+          for (int half = 0; ok && half < 2; ++half) {
+            const int t = 4 * i + 2 * prod + half, slot = t % C::kRing, ph = (t / C::kRing) & 1;
+            if (!(ok = mbar_wait(bar(C::kBarRingFull + slot), ph, w, kBSiteMmaQ))) break;
+            issue_rows_x_rows<128, BF16>(
+                elected, tmem_base + (prod ? C::kColDpt : C::kColSt) + b * 128,
+                smem_base + (prod ? C::kOffV : C::kOffK) + half * T::kTileBytes,
+                smem_base + C::kOffRing + slot * T::kTileBytes, half);
+            commit(C::kBarRingEmpty + slot);
+          }
+          if (ok) commit((prod ? C::kBarDptFull : C::kBarStFull) + b);
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    reg_inc<208>();
+    const int wg = warp >> 2;  // 0: q columns 0..63 of the tile, 1: 64..127
+    const int w4 = warp & 3;
+    const int r = w4 * 32 + lane;  // kv row in the tile = tensor-memory lane
+    const uint32_t lane_base = static_cast<uint32_t>(w4 * 32) << 16;
+    const float2 sc2 = make_float2(scale_log2, scale_log2);
+    const float2 scale2 = make_float2(scale, scale);
+    bool ok = true;
+    for (int i = 0; i < nq; ++i) {
+      const int b = i & 1, u = i >> 1;
+      const uint32_t tSt = tmem_base + lane_base + C::kColSt + b * 128 + wg * 64;
+      const uint32_t tDpt = tmem_base + lane_base + C::kColDpt + b * 128 + wg * 64;
+      const float* stats = reinterpret_cast<const float*>(smem + C::kOffStats + b * 1024);
+      const float4* nlse = reinterpret_cast<const float4*>(stats + wg * 64);        // -lse*log2e
+      const float4* ndlt = reinterpret_cast<const float4*>(stats + 128 + wg * 64);  // -delta
+      const size_t out_off = static_cast<size_t>(tile0 + i) * 2048 + wg * 1024 + r;
+      if (!(ok = mbar_wait_warp(bar(C::kBarStatsFull + b), u & 1, w, kBSiteCmpQ))) break;
+      if (!(ok = mbar_wait_warp(bar(C::kBarStFull + b), u & 1, w, kBSiteCmpSt))) break;
+      tc_fence_after();
+      float2 p[32];  // P^T for this thread's kv row, q columns wg*64 .. wg*64+63
+      {
+        uint32_t sr[64];
+        tmem_ld_x32(tSt, sr);
+        tmem_ld_x32(tSt + 32, sr + 32);
+        tmem_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(C::kBarStFree + b));  // St(i + 2) may overwrite the buffer
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l = nlse[c4];
+          float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4]), __uint_as_float(sr[4 * c4 + 1])),
+                                 sc2, make_float2(l.x, l.y));
+          float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4 + 2]), __uint_as_float(sr[4 * c4 + 3])),
+                                 sc2, make_float2(l.z, l.w));
+          p[2 * c4] = exp2_pair(t0, 2 * c4);
+          p[2 * c4 + 1] = exp2_pair(t1, 2 * c4 + 1);
+        }
+      }
+      if (i == 0 || kv_ragged) {
+        // diagonal tile: keep q >= kv; rows beyond the last key keep nothing
+        const int first = (jt * 128 + r >= Nk) ? 128 : (i == 0 ? r : 0);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          p[c].x = (wg * 64 + 2 * c >= first) ? p[c].x : 0.f;
+          p[c].y = (wg * 64 + 2 * c + 1 >= first) ? p[c].y : 0.f;
+        }
+      }
+      {
+        // P^T rounded to 16 bits, piece-major (see bwd_dkdv_kernel's spill store)
+        uint4* dst = p_scratch + out_off;
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc)
+          dst[pc * 128] = make_uint4(pack2<BF16>(p[4 * pc].x, p[4 * pc].y),
+                                     pack2<BF16>(p[4 * pc + 1].x, p[4 * pc + 1].y),
+                                     pack2<BF16>(p[4 * pc + 2].x, p[4 * pc + 2].y),
+                                     pack2<BF16>(p[4 * pc + 3].x, p[4 * pc + 3].y));
+      }
+      if (!(ok = mbar_wait_warp(bar(C::kBarDptFull + b), u & 1, w, kBSiteCmpDpt))) break;
+      tc_fence_after();
+      uint32_t dp[64];
+      tmem_ld_x32(tDpt, dp);
+      tmem_ld_x32(tDpt + 32, dp + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarDptFree + b));
+      uint32_t dsk[32];
+#pragma unroll
+      for (int c4 = 0; c4 < 16; ++c4) {
+        const float4 nd = ndlt[c4];
+        // dS = P * (dP - delta) * scale, scale folded in before the 16-bit rounding
+        float2 u0 = __fadd2_rn(make_float2(__uint_as_float(dp[4 * c4]), __uint_as_float(dp[4 * c4 + 1])),
+                               make_float2(nd.x, nd.y));
+        float2 u1 = __fadd2_rn(make_float2(__uint_as_float(dp[4 * c4 + 2]), __uint_as_float(dp[4 * c4 + 3])),
+                               make_float2(nd.z, nd.w));
+        u0 = __fmul2_rn(__fmul2_rn(p[2 * c4], u0), scale2);
+        u1 = __fmul2_rn(__fmul2_rn(p[2 * c4 + 1], u1), scale2);
+        dsk[2 * c4] = pack2<BF16>(u0.x, u0.y);
+        dsk[2 * c4 + 1] = pack2<BF16>(u1.x, u1.y);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(C::kBarStatsFree + b));  // the row statistics are consumed
+      {
+        uint4* dst = ds_scratch + out_off;
+#pragma unroll
+        for (int pc = 0; pc < 8; ++pc)
+          dst[pc * 128] = make_uint4(dsk[4 * pc], dsk[4 * pc + 1], dsk[4 * pc + 2], dsk[4 * pc + 3]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == C::kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <bool BF16>
+cudaError_t launch_scores_wide_t(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                                 const CUtensorMap& tv, const CUtensorMap& tdo, const float* rowstats,
+                                 void* p_scratch, void* ds_scratch, int* status,
+                                 cudaStream_t stream) {
+  using C = ScoresCfg;
+  auto kern = bwd_scores_wide_kernel<BF16>;
+  cudaError_t e =
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  dim3 grid((s.Nk + 127) / 128, s.H, s.B);  // one CTA per KV tile
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(
+      tq, tk, tv, tdo, rowstats, static_cast<uint4*>(p_scratch), static_cast<uint4*>(ds_scratch),
+      s.N, s.Nk, s.scale, s.scale * 1.4426950408889634f, status);
+  return cudaGetLastError();
 }
 
 template <int D, bool BF16, int MODE>
@@ -986,16 +1289,16 @@ cudaError_t launch_dkdv_t(const AttnShape& s, const CUtensorMap& tq, const CUten
   return cudaGetLastError();
 }
 
-template <int D, bool BF16>
-cudaError_t launch_dq_spill_t(const AttnShape& s, const void* ds_scratch, const CUtensorMap& tk,
-                              const CUtensorMap& tdq, int* status, cudaStream_t stream) {
-  using C = DqSpillCfg<D>;
-  auto kern = bwd_dq_spill_kernel<D, BF16>;
+template <int D, bool BF16, int FORM>
+cudaError_t launch_consume_t(const AttnShape& s, const void* scratch, const CUtensorMap& tb,
+                             const CUtensorMap& tout, int* status, cudaStream_t stream) {
+  using C = ConsumeCfg<D>;
+  auto kern = bwd_consume_kernel<D, BF16, FORM>;
   cudaError_t e =
       cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
   if (e != cudaSuccess) return e;
-  dim3 grid((s.N + 127) / 128, s.H, s.B);
-  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(static_cast<const uint4*>(ds_scratch), tk, tdq,
+  dim3 grid(((FORM == 2 ? s.N : s.Nk) + 127) / 128, s.H, s.B);  // one CTA per output tile
+  kern<<<grid, C::kThreads, C::kSmemBytes, stream>>>(static_cast<const uint4*>(scratch), tb, tout,
                                                      s.N, s.Nk, status);
   return cudaGetLastError();
 }
@@ -1071,18 +1374,39 @@ cudaError_t launch_bwd_dq(const AttnShape& s, const CUtensorMap& tq, const CUten
   return cudaErrorInvalidValue;
 }
 
-cudaError_t launch_bwd_dq_spill(const AttnShape& s, const void* ds_scratch, const CUtensorMap& tk,
-                                const CUtensorMap& tdq, int* status, cudaStream_t stream) {
-#define FA2_CASE(DD)                                                                         \
-  case DD:                                                                                   \
-    return s.dtype ? launch_dq_spill_t<DD, true>(s, ds_scratch, tk, tdq, status, stream)     \
-                   : launch_dq_spill_t<DD, false>(s, ds_scratch, tk, tdq, status, stream);
+cudaError_t launch_bwd_scores_wide(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                                   const CUtensorMap& tv, const CUtensorMap& tdo,
+                                   const float* rowstats, void* p_scratch, void* ds_scratch,
+                                   int* status, cudaStream_t stream) {
+  return s.dtype ? launch_scores_wide_t<true>(s, tq, tk, tv, tdo, rowstats, p_scratch, ds_scratch,
+                                              status, stream)
+                 : launch_scores_wide_t<false>(s, tq, tk, tv, tdo, rowstats, p_scratch, ds_scratch,
+                                               status, stream);
+}
+
+cudaError_t launch_bwd_consume(const AttnShape& s, int form, const void* scratch,
+                               const CUtensorMap& tb, const CUtensorMap& tout, int* status,
+                               cudaStream_t stream) {
+#define FA2_ARGS s, scratch, tb, tout, status, stream
+#define FA2_CASE(DD)                                                      \
+  case DD:                                                                \
+    return s.dtype ? launch_consume_t<DD, true, 2>(FA2_ARGS)              \
+                   : launch_consume_t<DD, false, 2>(FA2_ARGS);
+  if (s.D == 256) {
+    if (form == 0)
+      return s.dtype ? launch_consume_t<256, true, 0>(FA2_ARGS) : launch_consume_t<256, false, 0>(FA2_ARGS);
+    if (form == 1)
+      return s.dtype ? launch_consume_t<256, true, 1>(FA2_ARGS) : launch_consume_t<256, false, 1>(FA2_ARGS);
+    return s.dtype ? launch_consume_t<256, true, 2>(FA2_ARGS) : launch_consume_t<256, false, 2>(FA2_ARGS);
+  }
+  if (form != 2) return cudaErrorInvalidValue;
   switch (s.D) {
     FA2_CASE(32)
     FA2_CASE(64)
     FA2_CASE(128)
   }
 #undef FA2_CASE
+#undef FA2_ARGS
   return cudaErrorInvalidValue;
 }
 

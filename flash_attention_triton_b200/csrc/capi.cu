@@ -162,8 +162,13 @@ std::atomic<long long> g_spill_budget{8ll << 30};
 struct SpillPlan {
   int nb, nh;  // batch entries and heads per chunk
 };
-SpillPlan spill_plan(int B, int H, int N) {
-  const long long per_head = dstile_pairs(N, N) * 32768;
+// Scratch bytes per (batch, head) problem: one 32 KiB dS tile per (KV tile, Q tile) pair, and
+// a P tile as well for head dims above 128.
+long long spill_bytes_per_head(int N, int D) {
+  return dstile_pairs(N, N) * 32768 * (D > 128 ? 2 : 1);
+}
+SpillPlan spill_plan(int B, int H, int N, int D) {
+  const long long per_head = spill_bytes_per_head(N, D);
   const long long heads_fit = std::max<long long>(1, g_spill_budget.load() / per_head);
   if (heads_fit >= H)
     return SpillPlan{static_cast<int>(std::min<long long>(B, std::max<long long>(1, heads_fit / H))), H};
@@ -248,7 +253,6 @@ int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse
                                fa2_stream_t stream) {
   if (!o || !dout || !lse || !rowstats) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
-  if (D > 128) return FA2_ERR_HEAD_DIM;  // the backward stops at 128
   if (!aligned16(o) || !aligned16(dout) || !aligned16(rowstats)) return FA2_ERR_MISALIGNED;
   Strides so, sdo;
   if (int e = get_strides(strides, 0, B, H, N, D, &so)) return e;
@@ -266,11 +270,12 @@ int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float*
 }
 
 size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
-  if (deterministic == 1 || B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
-  if (deterministic == 2) {  // one 16-bit [128 x 128] dS tile per (KV tile, Q tile) pair of a chunk
-    const SpillPlan plan = spill_plan(B, H, N);
-    return static_cast<size_t>(plan.nb) * plan.nh * static_cast<size_t>(dstile_pairs(N, N)) * 32768;
+  if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
+  if (deterministic == 2 || D > 128) {  // 16-bit [128 x 128] tiles per (KV tile, Q tile) pair of a chunk
+    const SpillPlan plan = spill_plan(B, H, N, D);
+    return static_cast<size_t>(plan.nb) * plan.nh * static_cast<size_t>(spill_bytes_per_head(N, D));
   }
+  if (deterministic == 1) return 0;
   const size_t ntiles = (static_cast<size_t>(N) + 127) / 128;
   return static_cast<size_t>(B) * H * ntiles * 128 * padded_head_dim(D) * sizeof(float);
 }
@@ -281,8 +286,10 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
                     const long long* strides, fa2_stream_t stream) {
   if (!q || !k || !v || !dout || !rowstats || !dq || !dk || !dv) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
-  if (D > 128) return FA2_ERR_HEAD_DIM;  // the backward stops at 128
   if (Nk < 1 || Nk > N) return FA2_ERR_SHAPE;
+  // Head dims above 128 have one backward (scores kernel + three consumer kernels over two
+  // scratch tensors); it is deterministic and serves every value of `deterministic`.
+  if (D > 128) deterministic = 2;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(dout) || !aligned16(dq) ||
       !aligned16(dk) || !aligned16(dv) || !aligned16(rowstats))
     return FA2_ERR_MISALIGNED;
@@ -316,7 +323,7 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
     return static_cast<int>(launch_bwd_dq(s, tq, tk, tv, tdo, tdq, rowstats, d->status, st));
   }
   if (deterministic == 2) {
-    const SpillPlan plan = spill_plan(B, H, N);
+    const SpillPlan plan = spill_plan(B, H, N, D);
     if (plan.nb < B || plan.nh < H) {
       // more than one chunk: the same call on sub-ranges, one after the other on the stream
       // (they share the scratch), with the caller's strides spelled out
@@ -350,10 +357,23 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
     const long long pairs = static_cast<long long>(B) * H * dstile_pairs(N, Nk);
     if (pairs >= (1ll << 31)) return FA2_ERR_SHAPE;
     if (int e = make_map(&tdq, dq, dtype, B, H, N, D, sdq, 32)) return e;
+    if (D > 128) {
+      // P tiles first, dS tiles behind them
+      char* p_scratch = reinterpret_cast<char*>(dq_accum);
+      char* ds_scratch = p_scratch + static_cast<size_t>(pairs) * 32768;
+      cudaError_t ce = launch_bwd_scores_wide(s, tq, tk, tv, tdo, rowstats, p_scratch, ds_scratch,
+                                              d->status, st);
+      if (ce != cudaSuccess) return static_cast<int>(ce);
+      if ((ce = launch_bwd_consume(s, 0, p_scratch, tdo, tdv, d->status, st)) != cudaSuccess)
+        return static_cast<int>(ce);
+      if ((ce = launch_bwd_consume(s, 1, ds_scratch, tq, tdk, d->status, st)) != cudaSuccess)
+        return static_cast<int>(ce);
+      return static_cast<int>(launch_bwd_consume(s, 2, ds_scratch, tk, tdq, d->status, st));
+    }
     cudaError_t ce =
         launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum, 2, d->status, st);
     if (ce != cudaSuccess) return static_cast<int>(ce);
-    return static_cast<int>(launch_bwd_dq_spill(s, dq_accum, tk, tdq, d->status, st));
+    return static_cast<int>(launch_bwd_consume(s, 2, dq_accum, tk, tdq, d->status, st));
   }
   cudaError_t ce = cudaMemsetAsync(dq_accum, 0, fa2_bwd_workspace_bytes(B, H, N, D, 0), st);
   if (ce != cudaSuccess) return static_cast<int>(ce);

@@ -13,7 +13,7 @@ namespace fa2 {
 // and what the tensor-core shared-memory descriptors below describe.
 template <int D>
 struct Tile {
-  static_assert(D == 32 || D == 64 || D == 128, "head dim must be 32, 64 or 128");
+  static_assert(D == 32 || D == 64 || D == 128 || D == 256, "tile width must be 32, 64, 128 or 256");
   static constexpr int kRows = 128;
   static constexpr int kChunkElems = D >= 64 ? 64 : 32;
   static constexpr int kChunks = D / kChunkElems;
@@ -107,9 +107,22 @@ cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUt
                             const float* rowstats, float* dq_accum, int mode, int* status,
                             cudaStream_t stream);
 
-// dQ per Q tile from the spilled dS tiles, ascending KV order (deterministic).
-cudaError_t launch_bwd_dq_spill(const AttnShape& s, const void* ds_scratch, const CUtensorMap& tk,
-                                const CUtensorMap& tdq, int* status, cudaStream_t stream);
+// Head dim 256: P^T and dS^T of every (KV tile, Q tile) pair as 16-bit piece-major tiles into two
+// scratch tensors (pair numbering as in the spill mode); launch_bwd_consume forms 0, 1 and 2 then
+// give dV, dK and dQ.
+cudaError_t launch_bwd_scores_wide(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
+                                   const CUtensorMap& tv, const CUtensorMap& tdo,
+                                   const float* rowstats, void* p_scratch, void* ds_scratch,
+                                   int* status, cudaStream_t stream);
+
+// One output tile per CTA from spilled 16-bit score-gradient / probability tiles, one product
+// per tile pair in ascending order (deterministic):
+//   form 2: dQ(qt) = sum_j dS(j, qt) K_j     (scratch = dS tiles, tb = K, tout = dQ)
+//   form 0: dV(jt) = sum_i P(jt, i)^T dO_i   (scratch = P tiles,  tb = dO, tout = dV)  head dim 256
+//   form 1: dK(jt) = sum_i dS(jt, i)^T Q_i   (scratch = dS tiles, tb = Q,  tout = dK)  head dim 256
+cudaError_t launch_bwd_consume(const AttnShape& s, int form, const void* scratch,
+                               const CUtensorMap& tb, const CUtensorMap& tout, int* status,
+                               cudaStream_t stream);
 
 // (KV tile, Q tile) pairs of one head: KV tile t < nktiles meets Q tiles t .. ntiles-1.
 inline long long dstile_pairs(int N, int Nk) {

@@ -174,6 +174,7 @@ cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strid
     FA2_CASE(32)
     FA2_CASE(64)
     FA2_CASE(128)
+    FA2_CASE(256)
   }
 #undef FA2_CASE
   return cudaErrorInvalidValue;

@@ -110,4 +110,29 @@ __device__ __forceinline__ void issue_piecesT_x_tile(uint32_t elected, uint32_t 
              k > 0 ? 1u : accumulate);
 }
 
+// acc[128, D] (+)= A * B with A = a piece-major tile used the other way round: row r of the tile
+// is the M index and its columns are the reduction index (K-major, unswizzled: core matrices of
+// 8 rows x 16 bytes, 128 bytes apart along M and 2048 bytes apart along the reduction index);
+// B a staged [128, D] tile (MN-major).
+#ifndef FA2_NSK_LBO
+#define FA2_NSK_LBO 2048  /* stride between core matrices along the reduction (K) index */
+#define FA2_NSK_SBO 128   /* stride between core matrices along the M index */
+#endif
+template <int D, bool BF16>
+__device__ __forceinline__ void issue_pieces_x_tile(uint32_t elected, uint32_t d_tmem,
+                                                    uint32_t a_addr, uint32_t b_addr,
+                                                    uint32_t accumulate) {
+  using T = Tile<D>;
+  constexpr uint32_t idesc = make_idesc(128, D, BF16, false, true);
+  constexpr uint32_t a_hi = desc_hi_word(FA2_NSK_SBO, 0u);  // no swizzle
+  constexpr uint32_t b_hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
+  const uint32_t a_lo = desc_lo_word(a_addr, FA2_NSK_LBO), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
+#pragma unroll
+  for (int k = 0; k < 8; ++k)
+    if (elected)
+      mma_ss(d_tmem, desc_from_words(a_lo + ((k * 4096) >> 4), a_hi),
+             desc_from_words(b_lo + ((k * 2 * T::kAtomBytes) >> 4), b_hi), idesc,
+             k > 0 ? 1u : accumulate);
+}
+
 }  // namespace fa2

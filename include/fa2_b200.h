@@ -5,9 +5,11 @@
  * stream it is given and returns without synchronising (the one exception,
  * fa2_device_status, says so).  The caller owns every buffer.  All tensors are dense
  * row-major [B, H, N, D] (strides implied) on the current CUDA device; lse is dense fp32
- * [B, H, N].  D is a multiple of 8 between 8 and 128, for fa2_fwd up to 256 (32, 64, 128 and
- * 256 are the native tile widths; sizes in between run zero-padded to the next one through TMA
- * out-of-bounds fill, with no extra memory traffic); dtype 0 = fp16, 1 = bf16.
+ * [B, H, N].  D is a multiple of 8 between 8 and 256 (32, 64, 128 and 256 are the native tile
+ * widths; sizes in between run zero-padded to the next one through TMA out-of-bounds fill, with
+ * no extra memory traffic); dtype 0 = fp16, 1 = bf16.  Above D = 128 the backward has a single,
+ * deterministic strategy that needs the workspace fa2_bwd_workspace_bytes reports whatever
+ * `deterministic` says, and fa2_bwd_static_scratch is not available (FA2_ERR_WORKSPACE).
  *
  * Return value: 0 = success; negative = argument / environment error (table below);
  * positive = a cudaError_t from a launch or attribute call.
@@ -39,7 +41,7 @@ extern "C" {
 
 #define FA2_OK 0
 #define FA2_ERR_NULL_POINTER (-1)      /* a required pointer is NULL */
-#define FA2_ERR_HEAD_DIM (-2)          /* D not a multiple of 8 in [8, 256] (backward: [8, 128]) */
+#define FA2_ERR_HEAD_DIM (-2)          /* D not a multiple of 8 in [8, 256] */
 #define FA2_ERR_DTYPE (-3)             /* dtype not FA2_DTYPE_FP16 / FA2_DTYPE_BF16 */
 #define FA2_ERR_MISALIGNED (-4)        /* a tensor pointer is not 16-byte aligned */
 #define FA2_ERR_SHAPE (-5)             /* B, H or N <= 0, B*H > 65535, N too large, Nk not in [1, N] */

@@ -90,7 +90,7 @@ def test_backward_argument_errors_need_no_gpu():
     assert rc == -1
     rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], None, 1, 1, 128, 64, 0, None)
     assert rc == -1
-    rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], p[3], 1, 1, 128, 256, 0, None)
+    rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], p[3], 1, 1, 128, 264, 0, None)
     assert rc == -2
 
 
