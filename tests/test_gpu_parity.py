@@ -275,6 +275,7 @@ def test_forward_backward_with_head_dims_up_to_256(shape, dtype):
         (640, 384, 32, torch.float16),    # tile-aligned key count
         (200, 520, 64, torch.bfloat16),   # more keys than queries: the tail gets zero gradients
         (129, 1, 64, torch.float16),      # a single key
+        (700, 300, 256, torch.bfloat16),  # head dim above 128: scores + consumer kernels
     ],
 )
 def test_seqlen_q_differs_from_seqlen_k(nq, nk, d, dtype, mode, monkeypatch):
