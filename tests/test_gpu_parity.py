@@ -118,6 +118,31 @@ def test_spill_mode_chunks_change_no_bit(monkeypatch):
     assert (recompute["dq"].float() - whole["dq"].float()).abs().max() <= 2e-3
 
 
+@pytest.mark.parametrize("d", [64, 256])
+def test_spill_chunks_with_strided_tensors(d, monkeypatch):
+    """The chunks of the spill mode are sub-ranges of the caller's tensors addressed through the
+    caller's strides: [B, N, H, D] storage, fewer keys than queries, head dim 64 (one scratch) and
+    256 (two scratches), chunked by a small budget; same bits as in one piece, parity with the oracle."""
+    monkeypatch.setenv("FA2_B200_BWD_MODE", "spill")
+    g = torch.Generator().manual_seed(11)
+    q, do = (torch.randn(3, 500, 4, d, generator=g).to(torch.bfloat16).transpose(1, 2) for _ in range(2))
+    k, v = (torch.randn(3, 300, 4, d, generator=g).to(torch.bfloat16).transpose(1, 2) for _ in range(2))
+    ref = naive_attention(q, k, v, do)
+    lib = _lib.lib()
+    previous = lib.fa2_set_spill_budget(1 << 40)
+    try:
+        whole = run_api(q, k, v, do, None, True)
+        check_against(ref, whole, torch.bfloat16)
+        per_head = 10 * 32768 * (2 if d > 128 else 1)  # T = 4 Q tiles: 10 pairs
+        for budget in (3 * per_head, 9 * per_head):     # 2 + 2 heads per batch entry; 2 + 1 batch entries
+            lib.fa2_set_spill_budget(budget)
+            chunked = run_api(q, k, v, do, None, True)
+            for key in whole:
+                assert torch.equal(chunked[key], whole[key]), (key, budget)
+    finally:
+        lib.fa2_set_spill_budget(previous)
+
+
 def test_lse_and_rowstats_through_the_c_abi():
     """fa2_fwd's LSE and fa2_bwd_preprocess's tile-blocked (-lse*log2e, -delta) array, ragged N."""
     b, h, n, d = 2, 3, 300, 64
