@@ -327,6 +327,17 @@ def main():
     if st != 0:
         raise RuntimeError(f"kernel status word {st:#x} after warm-up")
 
+    # Kernels of this library per step: forward, preprocess and the backward-main kernels of the
+    # mode (atomic: fused kernel + convert; recompute: dK/dV + dQ; spill: dK/dV + dQ per chunk of
+    # the scratch budget; head dims above 128: scores + three consumers per chunk).
+    if mode == 2 and wsb:
+        tiles = (n + 127) // 128
+        per_head = tiles * (tiles + 1) // 2 * 32768 * (2 if d > 128 else 1)
+        chunks = -(-lb * lh * per_head // wsb)
+        launches_per_step = 2 + chunks * (4 if d > 128 else 2)
+    else:
+        launches_per_step = 4
+
     # ------------------------------------------------------------ timed region (device-resident)
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -469,7 +480,7 @@ def main():
                              "nominal_2250": value / world / 2250.0, "source": peaks["source"]},
             "clocks": clocks.summary(),
             "sustained": sustained,
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline,
             "e2e": e2e,
         }
