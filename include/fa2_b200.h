@@ -65,6 +65,10 @@ const char* fa2_strerror(int code);
  * Forward: O = softmax_causal(scale * Q K^T) V, lse[b,h,i] = log sum_j exp(scale * s_ij)
  * (natural log).  Replaces _flash_attention_forward / _forward_kernel; unlike the
  * reference (flash_attention_2.py:98-100) lse is not padded and no scratch buffer is used.
+ * The kernel runs one CTA per SM; the CTAs draw their work items from a device counter that
+ * the library takes from a ring of 1024 (a new one per call, so calls on different streams do
+ * not share one).  A call captured into a CUDA graph keeps its counter: replays of that graph
+ * must not overlap each other.
  */
 int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
             int B, int H, int N, int D, int dtype, float scale, fa2_stream_t stream);
