@@ -143,6 +143,38 @@ def test_spill_chunks_with_strided_tensors(d, monkeypatch):
         lib.fa2_set_spill_budget(previous)
 
 
+def test_random_shapes_against_the_oracle(monkeypatch):
+    """A seeded sweep over shapes the fixed cases do not name: sequence lengths 1..700 for queries
+    and keys, head dims 8..256 in steps of 8, both dtypes, every dQ strategy, dense and
+    [B, N, H, D]-strided storage."""
+    import random
+
+    rng = random.Random(1234)
+    for case in range(36):
+        nq = rng.choice([1, 2, 63, 64, 65, 127, 128, 129, 255, 256, 257]) if case % 3 == 0 else rng.randint(1, 700)
+        nk = nq if case % 2 == 0 else rng.randint(1, 700)
+        d = 8 * rng.randint(1, 32)
+        b, h = rng.randint(1, 3), rng.randint(1, 3)
+        dtype = rng.choice([torch.float16, torch.bfloat16])
+        mode = rng.choice(["spill", "recompute", "atomic"])
+        strided = rng.random() < 0.4
+        monkeypatch.setenv("FA2_B200_BWD_MODE", mode)
+        g = torch.Generator().manual_seed(case)
+        if strided:
+            q, do = (torch.randn(b, nq, h, d, generator=g).to(dtype).transpose(1, 2) for _ in range(2))
+            k, v = (torch.randn(b, nk, h, d, generator=g).to(dtype).transpose(1, 2) for _ in range(2))
+        else:
+            q, do = (torch.randn(b, h, nq, d, generator=g).to(dtype) for _ in range(2))
+            k, v = (torch.randn(b, h, nk, d, generator=g).to(dtype) for _ in range(2))
+        ref = naive_attention(q, k, v, do)
+        got = run_api(q, k, v, do, None, mode != "atomic")
+        try:
+            check_against(ref, got, dtype)
+        except AssertionError as exc:
+            raise AssertionError(f"case {case}: nq={nq} nk={nk} d={d} b={b} h={h} {dtype} {mode} "
+                                 f"strided={strided}: {exc}") from exc
+
+
 def test_lse_and_rowstats_through_the_c_abi():
     """fa2_fwd's LSE and fa2_bwd_preprocess's tile-blocked (-lse*log2e, -delta) array, ragged N."""
     b, h, n, d = 2, 3, 300, 64
