@@ -48,6 +48,14 @@ def run_api(q, k, v, do, scale, det, dev=DEV):
     return {"o": out.detach(), "dq": qd.grad, "dk": kd.grad, "dv": vd.grad}
 
 
+def run_api_no_sync(q, k, v, do, scale, det, dev=DEV):
+    """Like run_api on the current stream, without reading the status word (which synchronises)."""
+    qd, kd, vd = (t.to(dev, non_blocking=True).requires_grad_(True) for t in (q, k, v))
+    out = flash_attention_v2(qd, kd, vd, scale, deterministic=det)
+    out.backward(do.to(dev, non_blocking=True))
+    return {"o": out.detach(), "dq": qd.grad, "dk": kd.grad, "dv": vd.grad}
+
+
 def check_against(ref, got, dtype, keys=("o", "dq", "dk", "dv")):
     for key in keys:
         g = got[key].detach().cpu().double()
@@ -173,6 +181,27 @@ def test_random_shapes_against_the_oracle(monkeypatch):
         except AssertionError as exc:
             raise AssertionError(f"case {case}: nq={nq} nk={nk} d={d} b={b} h={h} {dtype} {mode} "
                                  f"strided={strided}: {exc}") from exc
+
+
+def test_calls_on_two_streams_do_not_disturb_each_other():
+    """Forward and backward of two different problems issued alternately on two CUDA streams (the
+    forward kernels draw work from per-call counters) give the bits of the serial runs."""
+    a = make_inputs((2, 4, 1500, 128), torch.bfloat16, seed=21)
+    b = make_inputs((3, 2, 900, 64), torch.float16, seed=22)
+    want_a = run_api(*a, None, True)
+    want_b = run_api(*b, None, True)
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    for _ in range(3):
+        outs = []
+        for stream, inputs in ((s1, a), (s2, b), (s1, b), (s2, a)):
+            with torch.cuda.stream(stream):
+                outs.append(run_api_no_sync(*inputs, None, True))
+        torch.cuda.synchronize()
+        assert _lib.device_status() == 0
+        for got, want in zip(outs, (want_a, want_b, want_b, want_a)):
+            for key in want:
+                assert torch.equal(got[key], want[key]), key
 
 
 def test_lse_and_rowstats_through_the_c_abi():
