@@ -3,11 +3,11 @@
 The reference has no golden files and needs a CUDA device through its public API, but its
 three Triton kernels run unmodified on CPU tensors under Triton's interpreter
 (``TRITON_INTERPRET=1``).  This script imports flash-attention-triton from ``--reference``
-(default ``/root/reference/src``), runs ``_forward_kernel`` and ``_flash_attention_backward`` on
+(a checkout of the project, its ``src`` directory), runs ``_forward_kernel`` and ``_flash_attention_backward`` on
 seeded inputs and stores inputs + outputs as compressed ``.npz`` next to this file.  The
 tests only read the ``.npz`` files; they never need the reference.
 
-Usage:  python tests/golden/make_golden.py [--reference /path/to/flash-attention-triton/src]
+Usage:  python tests/golden/make_golden.py --reference /path/to/flash-attention-triton/src [--only NAME]
 """
 
 from __future__ import annotations
@@ -36,7 +36,7 @@ CASES = [
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference/src")
+    ap.add_argument("--reference", required=True, help="path to flash-attention-triton/src")
     ap.add_argument("--only", default="", help="substring of the case names to (re)generate")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
