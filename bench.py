@@ -1,7 +1,7 @@
 """Benchmark of the causal attention forward + backward hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload c3|c2|c5|c4] [--deterministic] [--scaling weak|strong]
+                    [--workload c3|c2|c5|c4|d256] [--deterministic] [--scaling weak|strong]
 
 A "step" is one forward + backward (forward, preprocess, backward main, plus memset/convert
 in the atomic mode) over one batch of seeded synthetic inputs of the workload's shape.
@@ -54,6 +54,10 @@ WORKLOADS = {
     "c3": (2, 32, 8192, 128, torch.bfloat16, 1.0, None),
     "c4": (1, 16, 32768, 128, torch.bfloat16, 1.0, None),
     "c5": (8, 12, 4095, 32, torch.float16, 3.0, 0.5),
+    # head dim 256 (the reference's max_headdim): forward on the split plan, backward through the
+    # scores + consumer kernels; d256small for profiler captures
+    "d256": (2, 16, 8192, 256, torch.bfloat16, 1.0, None),
+    "d256small": (1, 16, 8192, 256, torch.bfloat16, 1.0, None),
     # reduced C3 (same N, d, dtype; 24 instead of 64 batch*heads) for profiler captures
     "c3small": (1, 24, 8192, 128, torch.bfloat16, 1.0, None),
 }
@@ -372,9 +376,10 @@ def main():
     fwd_tf = my_fwd_flops / (ms_fwd * 1e-3) / 1e12
     pre_bytes = 2.0 * lb * lh * n * d * 2 + lb * lh * n * 4 * 3
     roofline = {
-        "kernel": ("bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert",
-                   "bwd_dkdv_kernel + bwd_dq_kernel (S, dP recomputed)",
-                   "bwd_dkdv_kernel (dS tiles spilled) + bwd_dq_spill_kernel")[mode],
+        "kernel": "bwd_scores_wide_kernel + bwd_consume_kernel x3 (dV, dK, dQ)" if d > 128 else (
+            "bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert",
+            "bwd_dkdv_kernel + bwd_dq_kernel (S, dP recomputed)",
+            "bwd_dkdv_kernel (dS tiles spilled) + bwd_consume_kernel (dQ)")[mode],
         "bound": "tensor", "achieved": bwd_tf, "peak": peaks["bf16"], "unit": "TFLOP/s",
         "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} burst bf16 GEMM",
         "traffic": traffic_bytes(d, mode, lb * lh, n),
