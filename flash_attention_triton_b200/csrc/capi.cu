@@ -201,7 +201,8 @@ const char* fa2_strerror(int code) {
     case FA2_ERR_DEVICE_STATUS: return "a kernel abandoned a bounded wait (see fa2_device_status)";
     case FA2_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
     case FA2_ERR_SCALE: return "softmax scale must be finite and > 0";
-    case FA2_ERR_WORKSPACE: return "dq_accum workspace is required when deterministic == 0";
+    case FA2_ERR_WORKSPACE:
+      return "this backward mode needs the dq_accum workspace (fa2_bwd_workspace_bytes)";
     case FA2_ERR_STRIDE:
       return "strides must be positive multiples of 8 elements (16 bytes), row stride >= D";
     case FA2_ERR_TOO_LARGE: return "problem exceeds the built-in scratch (B*H*ceil(N/128) > 4096)";

@@ -49,7 +49,7 @@ extern "C" {
 #define FA2_ERR_DEVICE_STATUS (-7)     /* a kernel gave up on a bounded wait */
 #define FA2_ERR_DRIVER (-8)            /* cuTensorMapEncodeTiled unavailable or failed */
 #define FA2_ERR_SCALE (-9)             /* softmax scale not finite or not > 0 */
-#define FA2_ERR_WORKSPACE (-10)        /* dq_accum is NULL although deterministic == 0 */
+#define FA2_ERR_WORKSPACE (-10)        /* dq_accum is NULL although the mode needs a workspace */
 #define FA2_ERR_TOO_LARGE (-11)        /* fa2_bwd_static_scratch: B*H*ceil(N/128) > 4096 */
 #define FA2_ERR_STRIDE (-12)           /* a stride is <= 0, not a multiple of 8 elements, or row < D */
 
