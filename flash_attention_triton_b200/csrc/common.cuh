@@ -100,7 +100,7 @@ cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strid
 // (dq_accum layout: [bh][t][w = 4][k = D/4][lane = 32][4] floats, holding element
 // (row 128*t + 32*w + lane, col 4*k + 0..3)); mode 2 also stores every 16-bit dS^T tile to the
 // scratch tensor dq_accum then points to (32 KiB per (KV tile, Q tile) pair, pairs numbered
-// per head KV tile by KV tile, see dstile_pairs), from which launch_bwd_dq_spill forms dQ.
+// per head KV tile by KV tile, see dstile_pairs), from which launch_bwd_consume (form 2) forms dQ.
 cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                             const CUtensorMap& tv, const CUtensorMap& tdo,
                             const CUtensorMap& tdk, const CUtensorMap& tdv,
