@@ -54,6 +54,33 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
                : "memory");
 }
 
+// The transposed-score kernels (bwd_dkdv_kernel, bwd_scores_wide_kernel) give each thread one kv
+// row and 64 q columns of a tile.  probabilities_of_row: p = 2^(s * c - lse2[q]) from the raw
+// scores `sr` and the negated, log2-scaled row statistics of the 64 columns (`nlse`, read with
+// warp-wide broadcasts).  mask_row: keep only the q columns >= `first` (128 keeps nothing).
+__device__ __forceinline__ void probabilities_of_row(const uint32_t (&sr)[64], const float4* nlse,
+                                                     float2 sc2, float2 (&p)[32]) {
+#pragma unroll
+  for (int c4 = 0; c4 < 16; ++c4) {
+    const float4 l = nlse[c4];
+    const float2 t0 = __ffma2_rn(
+        make_float2(__uint_as_float(sr[4 * c4]), __uint_as_float(sr[4 * c4 + 1])), sc2,
+        make_float2(l.x, l.y));
+    const float2 t1 = __ffma2_rn(
+        make_float2(__uint_as_float(sr[4 * c4 + 2]), __uint_as_float(sr[4 * c4 + 3])), sc2,
+        make_float2(l.z, l.w));
+    p[2 * c4] = exp2_pair(t0, 2 * c4);
+    p[2 * c4 + 1] = exp2_pair(t1, 2 * c4 + 1);
+  }
+}
+__device__ __forceinline__ void mask_row(float2 (&p)[32], int first_column, int column0) {
+#pragma unroll
+  for (int c = 0; c < 32; ++c) {
+    p[c].x = (column0 + 2 * c >= first_column) ? p[c].x : 0.f;
+    p[c].y = (column0 + 2 * c + 1 >= first_column) ? p[c].y : 0.f;
+  }
+}
+
 // Epilogue helper: one warp converts its 32 rows of a [128, D] fp32 accumulator to 16 bits,
 // stages them swizzled in `stage` (a free tile buffer) and stores them with one TMA per chunk.
 template <int D, bool BF16>
@@ -425,26 +452,12 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
         tmem_ld_x32(tSt + 32, sr + 32);
         tmem_wait_ld();
         FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 7);
-#pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 l = nlse[c4];
-          float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4]), __uint_as_float(sr[4 * c4 + 1])),
-                                 sc2, make_float2(l.x, l.y));
-          float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4 + 2]), __uint_as_float(sr[4 * c4 + 3])),
-                                 sc2, make_float2(l.z, l.w));
-          p[2 * c4] = exp2_pair(t0, 2 * c4);
-          p[2 * c4 + 1] = exp2_pair(t1, 2 * c4 + 1);
-        }
+        probabilities_of_row(sr, nlse, sc2, p);
       }
       if (ii == 0 || kv_ragged) {
         // diagonal tile: keep q >= kv; rows beyond the last key (zero-filled K, V) keep nothing,
         // so that a huge 2^(-lse) never meets their zeros
-        const int first = (jt * 128 + r >= Nk) ? 128 : (ii == 0 ? r : 0);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          p[c].x = (wg * 64 + 2 * c >= first) ? p[c].x : 0.f;
-          p[c].y = (wg * 64 + 2 * c + 1 >= first) ? p[c].y : 0.f;
-        }
+        mask_row(p, (jt * 128 + r >= Nk) ? 128 : (ii == 0 ? r : 0), wg * 64);
       }
       {
         uint32_t pk[32];
@@ -1183,25 +1196,11 @@ __global__ void __launch_bounds__(ScoresCfg::kThreads, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(C::kBarStFree + b));  // St(i + 2) may overwrite the buffer
-#pragma unroll
-        for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 l = nlse[c4];
-          float2 t0 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4]), __uint_as_float(sr[4 * c4 + 1])),
-                                 sc2, make_float2(l.x, l.y));
-          float2 t1 = __ffma2_rn(make_float2(__uint_as_float(sr[4 * c4 + 2]), __uint_as_float(sr[4 * c4 + 3])),
-                                 sc2, make_float2(l.z, l.w));
-          p[2 * c4] = exp2_pair(t0, 2 * c4);
-          p[2 * c4 + 1] = exp2_pair(t1, 2 * c4 + 1);
-        }
+        probabilities_of_row(sr, nlse, sc2, p);
       }
       if (i == 0 || kv_ragged) {
         // diagonal tile: keep q >= kv; rows beyond the last key keep nothing
-        const int first = (jt * 128 + r >= Nk) ? 128 : (i == 0 ? r : 0);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          p[c].x = (wg * 64 + 2 * c >= first) ? p[c].x : 0.f;
-          p[c].y = (wg * 64 + 2 * c + 1 >= first) ? p[c].y : 0.f;
-        }
+        mask_row(p, (jt * 128 + r >= Nk) ? 128 : (i == 0 ? r : 0), wg * 64);
       }
       {
         // P^T rounded to 16 bits, piece-major (see bwd_dkdv_kernel's spill store)
