@@ -103,8 +103,9 @@ def _flash_attention_forward(
 
 #: dQ strategies of the C library (the ``deterministic`` argument of ``fa2_bwd``)
 _MODE_ATOMIC, _MODE_RECOMPUTE, _MODE_SPILL = 0, 1, 2
-#: the spill mode keeps 32 KiB per tile pair; beyond this much per head it is not used
-_SPILL_MAX_BYTES_PER_HEAD = 2 << 30
+#: the spill mode keeps 32 KiB per tile pair; beyond this much per head (the library's default
+#: scratch bound: one head must fit) it is not used
+_SPILL_MAX_BYTES_PER_HEAD = 8 << 30
 
 
 def _backward_mode(deterministic: bool, headdim: int, seqlen_q: int) -> int:
