@@ -225,8 +225,6 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
   const int nktiles = (Nk + 127) >> 7;
   const int tile0 = bh * dstile_count(ntiles, nktiles) + dstile_count(ntiles, jt);
   (void)tile0;
-  const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;  // FA2_TRACE_EVENT only
-  (void)traced;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(C::kBarKV), 1);
@@ -329,7 +327,6 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
           if (!(ok = mbar_wait(bar(C::kBarDOFull + s), ph, w, kBSiteMmaDO))) break;
           if (!(ok = mbar_wait(bar(C::kBarPtReady), ii & 1, w, kBSiteMmaPt))) break;
           tc_fence_after();
-          FA2_TRACE_EVENT(traced && elected, ii * 16 + 0);
           issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDV, tmem_base + C::kColSt, 64, doa,
                                      ii > 0);  // dV += Pt dO_i
           commit(C::kBarDOEmpty + s);
@@ -340,7 +337,6 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
             commit(C::kBarStFull);
             commit(C::kBarQEmpty + s1);
           }
-          FA2_TRACE_EVENT(traced && elected, ii * 16 + 1);
           ph ^= s;
           s ^= 1;
         }
@@ -365,7 +361,6 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
             }
           }
           tc_fence_after();
-          FA2_TRACE_EVENT(traced && elected, ii * 16 + 2);
           issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDK, tmem_base + C::kColDpt, 64, qa,
                                      ii > 0);  // dK += dSt Q_i
           commit(C::kBarQEmpty + s);
@@ -375,19 +370,16 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
             issue_tileT_x_tile<D, BF16>(elected, tmem_base + C::kColDpt, smem_base + C::kOffDS, ka);
             commit(C::kBarDqFull);
           }
-          FA2_TRACE_EVENT(traced && elected, ii * 16 + 3);
           if (ii + 1 < nq) {
             if constexpr (FUSE) {
               if (!(ok = mbar_wait(bar(C::kBarDqDrained), ii & 1, w, kBSiteMmaDrain))) break;
               tc_fence_after();
-              FA2_TRACE_EVENT(traced && elected, ii * 16 + 4);
             }
             if (!(ok = mbar_wait(bar(C::kBarDOFull + s1), ph1, w, kBSiteMmaDO))) break;
             issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColDpt, va,
                                        smem_base + C::kOffDO + s1 * T::kTileBytes);  // dPt(i+1)
             commit(C::kBarDptFull);
             commit(C::kBarDOEmpty + s1);
-            FA2_TRACE_EVENT(traced && elected, ii * 16 + 5);
           }
           ph ^= s;
           s ^= 1;
@@ -404,7 +396,6 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
     for (int ii = 0; ii < nq; ++ii) {
       if (!mbar_wait_warp(bar(C::kBarDqFull), ii & 1, w, kBSiteRedDq)) break;
       tc_fence_after();
-      FA2_TRACE_EVENT(traced && warp == 8 && lane == 0, ii * 16 + 11);
       const int qt = jt + ii;
       float* dst = dq_accum + (((static_cast<size_t>(bh) * ntiles + qt) * 4 + w4) * (D / 4)) * 128 +
                    lane * 4;
@@ -417,12 +408,10 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarDqDrained));
-      FA2_TRACE_EVENT(traced && warp == 8 && lane == 0, ii * 16 + 12);
 #pragma unroll
       for (int k = 0; k < D / 4; ++k)
         red_add_v4(dst + k * 128, __uint_as_float(v[4 * k]), __uint_as_float(v[4 * k + 1]),
                    __uint_as_float(v[4 * k + 2]), __uint_as_float(v[4 * k + 3]));
-      FA2_TRACE_EVENT(traced && warp == 8 && lane == 0, ii * 16 + 13);
     }
   } else {
     // ---------------------------------------------------------------- compute groups
@@ -444,14 +433,12 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
       if (!(ok = mbar_wait_warp(bar(C::kBarQFull + s), ph, w, kBSiteCmpQ))) break;
       if (!(ok = mbar_wait_warp(bar(C::kBarStFull), ii & 1, w, kBSiteCmpSt))) break;
       tc_fence_after();
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 6);
       float2 p[32];  // P^T for this thread's kv row, q columns wg*64 .. wg*64+63
       {
         uint32_t sr[64];
         tmem_ld_x32(tSt, sr);
         tmem_ld_x32(tSt + 32, sr + 32);
         tmem_wait_ld();
-        FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 7);
         probabilities_of_row(sr, nlse, sc2, p);
       }
       if (ii == 0 || kv_ragged) {
@@ -469,11 +456,9 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarPtReady));
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 8);
 
       if (!(ok = mbar_wait_warp(bar(C::kBarDptFull), ii & 1, w, kBSiteCmpDpt))) break;
       tc_fence_after();
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 9);
       uint32_t dsk[32];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -520,7 +505,6 @@ __global__ void __launch_bounds__(DkdvCfg<D, MODE>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarDsReady));
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, ii * 16 + 10);
     }
     // epilogue: group 0 stores dV, group 1 stores dK, staged through the idle dO / Q buffers
     if (ok && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
@@ -612,8 +596,6 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
   const int bh = hc.b * static_cast<int>(gridDim.y) + hc.h;
   const int nktiles = (Nk + 127) >> 7;               // N = query rows, Nk <= N = key rows
   const int nkv = qt + 1 < nktiles ? qt + 1 : nktiles;  // KV tiles 0 .. min(qt, last)
-  const bool traced = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;  // FA2_TRACE_EVENT only
-  (void)traced;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(C::kBarQ), 1);
@@ -707,13 +689,11 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
           if (!(ok = mbar_wait(bar(C::kBarDpConsumed), (j - 1) & 1, w, kBSiteMmaDrain))) break;
           tc_fence_after();
         }
-        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 0);
         if (!(ok = mbar_wait(bar(C::kBarVFull + vs), vph, w, kBSiteMmaDO))) break;
         issue_rows_x_rows<D, BF16>(elected, tmem_base + C::kColDp, doa,
                                    smem_base + C::kOffV + vs * T::kTileBytes);
         commit(C::kBarDpFull);
         commit(C::kBarVEmpty + vs);  // V is free once dP has read it
-        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 1);
         if (++vs == C::kVStages) {
           vs = 0;
           vph ^= 1;
@@ -740,7 +720,6 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
                                    smem_base + C::kOffK + ks * T::kTileBytes);
         commit(C::kBarSFull + (j & 1));
         commit(C::kBarKEmpty + ks);
-        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 4);
         if (++ks == C::kKStages) {
           ks = 0;
           kph ^= 1;
@@ -758,13 +737,11 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
         if (!(ok = mbar_wait(bar(C::kBarKFull + ks), kph, w, kBSiteMmaKV))) break;
         if (!(ok = mbar_wait(bar(C::kBarDsReady), j & 1, w, kBSiteMmaDs))) break;
         tc_fence_after();
-        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 2);
         // A = 16-bit dS over score buffer j%2, B = K_j as MN-major tile
         issue_tmem_x_tile<D, BF16>(elected, tmem_base + C::kColDQ, tmem_base + C::kColS + (j & 1) * 128,
                                    64, smem_base + C::kOffK + ks * T::kTileBytes, j > 0);
         commit(C::kBarDqDone + (j & 1));
         commit(C::kBarKEmpty + ks);
-        FA2_TRACE_EVENT(traced && elected, 8192 + j * 16 + 3);
         if (++ks == C::kKStages) {
           ks = 0;
           kph ^= 1;
@@ -793,7 +770,6 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
       const uint32_t tS = tmem_base + lane_base + C::kColS + (j & 1) * 128 + wg * 64;
       if (!(ok = mbar_wait_warp(bar(C::kBarSFull + (j & 1)), (j >> 1) & 1, w, kBSiteCmpSt))) break;
       tc_fence_after();
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 6);
       float2 p[32];
       {
         uint32_t sr[64];
@@ -817,10 +793,8 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
           p[c].y = (wg * 64 + 2 * c + 1 <= last) ? p[c].y : 0.f;
         }
       }
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 7);
       if (!(ok = mbar_wait_warp(bar(C::kBarDpFull), j & 1, w, kBSiteCmpDpt))) break;
       tc_fence_after();
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 8);
       uint32_t dp[64];
       tmem_ld_x32(tDp, dp);
       tmem_ld_x32(tDp + 32, dp + 32);
@@ -828,7 +802,6 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarDpConsumed));
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 9);
       uint32_t dsk[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
@@ -842,7 +815,6 @@ __global__ void __launch_bounds__(DqCfg<D>::kThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarDsReady));
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, 8192 + j * 16 + 10);
     }
     if (ok && wg == 0 && mbar_wait_warp(bar(C::kBarDone), 0, w, kBSiteCmpDone)) {
       tc_fence_after();
@@ -1320,12 +1292,6 @@ cudaError_t launch_dq_t(const AttnShape& s, const CUtensorMap& tq, const CUtenso
 }
 
 }  // namespace
-
-#ifdef FA2_TRACE
-extern "C" int fa2_trace_read_bwd(long long* out, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n));
-}
-#endif
 
 cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                             const CUtensorMap& tv, const CUtensorMap& tdo,

@@ -14,9 +14,12 @@ namespace fa2 {
 
 // One status word per device: kernels write here when a bounded wait expires.
 __device__ int g_status_word;
-// Work counters of the tile-fetching kernels.  Every launch takes the next slot of this ring
-// and zeroes it on its stream, so launches that overlap on the device do not share a counter
-// (unless more than kWorkCounterSlots of them are in flight at once).
+// Work counters of the tile-fetching kernels.  Every launch takes the next slot of this ring, so
+// launches that overlap on the device do not share a counter (unless more than
+// kWorkCounterSlots of them are in flight at once).  No launch zeroes its slot: the slots are
+// zero at module load and every kernel puts its counter back to zero when it draws its last
+// number (fetch_work_item), so a slot is only left non-zero by a kernel that did not run to
+// its end.
 constexpr int kWorkCounterSlots = 1024;
 __device__ unsigned int g_work_counters[kWorkCounterSlots];
 
@@ -473,6 +476,13 @@ extern "C" int fa2_bwd_static_scratch(const void* q, const void* k, const void* 
                                       fa2_stream_t stream) {
   if (!q || !k || !v || !o || !dout || !lse || !dq || !dk || !dv) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
+  // Everything fa2_bwd would refuse is refused here, before the first launch: the preprocess
+  // kernel writes the shared array, and a call that is going to fail must not touch it.
+  if (D > 128) return FA2_ERR_WORKSPACE;  // that backward needs a caller workspace
+  if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || !aligned16(dout) ||
+      !aligned16(dq) || !aligned16(dk) || !aligned16(dv))
+    return FA2_ERR_MISALIGNED;
   const long long tiles = static_cast<long long>(B) * H * ((N + 127) / 128);
   if (tiles > kStaticRowstatTiles) return FA2_ERR_TOO_LARGE;
   float* rowstats = nullptr;

@@ -176,8 +176,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const int n0 = qt0 + 1 < nktiles ? qt0 + 1 : nktiles;
     const int n1 = has1 ? (qt1 + 1 < nktiles ? qt1 + 1 : nktiles) : 0;
     const int nkv = n1 > n0 ? n1 : n0;
-    const bool traced = item == 0;  // used by FA2_TRACE_EVENT only
-    (void)traced;
 
   if (warp >= 8) {
     reg_dec<72>();  // whole warpgroup (warps 8-11) gives registers to the softmax groups
@@ -256,7 +254,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
             if (!(ok = mbar_wait(bar(C::kBarSFree + prev_i), prev_ph, w, kSiteMmaSFree))) break;
             tc_fence_after();
           }
-          FA2_TRACE_EVENT(traced && elected, j * 16 + 4 + i);
           if constexpr (WIDE) {
             // S = Q_lo K_lo^T + Q_hi K_hi^T: the Q slots hold the halves, K arrives half by half
             for (int half = 0; ok && half < 2; ++half) {
@@ -274,7 +271,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
                                         smem_base + C::kOffK + ks * T::kTileBytes);
           }
           if (elected) mma_commit(bar(C::kBarSFull + i));
-          FA2_TRACE_EVENT(traced && elected, j * 16 + 0 + 2 * i);
           prev_i = i;
           prev_ph = j & 1;
         }
@@ -304,7 +300,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
           if (j >= (i == 0 ? n0 : n1)) continue;
           if (!(ok = mbar_wait(bar(C::kBarPFull + i), j & 1, w, kSiteMmaP))) break;
           tc_fence_after();
-          FA2_TRACE_EVENT(traced && elected, j * 16 + 6 + i);
           if constexpr (WIDE) {
             // O_lo += P V_lo, O_hi += P V_hi: the O0 / O1 columns hold the two halves of O
             for (int half = 0; ok && half < 2; ++half) {
@@ -322,7 +317,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
                                         smem_base + C::kOffV + vs * T::kTileBytes, j > 0);
           }
           if (elected) mma_commit(bar(C::kBarPvDone + i));
-          FA2_TRACE_EVENT(traced && elected, j * 16 + 1 + 2 * i);
         }
         if (!ok) break;
         if constexpr (!WIDE) {
@@ -348,7 +342,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     for (int j = 0; j < nj; ++j) {
       if (!(ok = mbar_wait_warp(bar(C::kBarSFull + wg), j & 1, w, kSiteSoftS))) break;
       tc_fence_after();
-      FA2_TRACE_EVENT(traced && (warp & 3) == 0 && lane == 0, j * 16 + (wg ? 13 : 8));
       uint32_t sr[128];
       tmem_ld_x32(tS + 0, sr + 0);
       tmem_ld_x32(tS + 32, sr + 32);
@@ -358,8 +351,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarSFree + wg));  // S may be overwritten now
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, j * 16 + 9);
-      FA2_TRACE_EVENT(traced && lane == 0, 8192 + j * 16 + 8 + warp);
       float* s = reinterpret_cast<float*>(sr);
       if (j == qt || j * 128 + 128 > Nk) {
         // diagonal tile: keep col <= row; last KV tile: drop the columns beyond the last key
@@ -399,7 +390,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
           }
         }
       }
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, j * 16 + 10);
       // p = 2^(s*c - m*c) with packed fp32x2 FMAs; row sum in four independent packed chains.
       const float2 sc2 = make_float2(scale_log2, scale_log2);
       const float2 nm2 = make_float2(-m_run * scale_log2, -m_run * scale_log2);
@@ -417,7 +407,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
         acc[c & 3] = __fadd2_rn(acc[c & 3], t);
         pk[c] = pack2<BF16>(t.x, t.y);
       }
-      FA2_TRACE_EVENT(traced && warp == 0 && lane == 0, j * 16 + 11);
       if (j > 0 && !pv_waited) {
         // P_i still feeds O_i += P_i(j-1) V_(j-1) until that product has completed
         if (!(ok = mbar_wait_warp(bar(C::kBarPvDone + wg), (j - 1) & 1, w, kSiteSoftPv))) break;
@@ -428,7 +417,6 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(C::kBarPFull + wg));
-      FA2_TRACE_EVENT(traced && (warp & 3) == 0 && lane == 0, j * 16 + (wg ? 14 : 12));
       const float2 a01 = __fadd2_rn(acc[0], acc[1]), a23 = __fadd2_rn(acc[2], acc[3]);
       l_run += (a01.x + a01.y) + (a23.x + a23.y);
     }
@@ -509,12 +497,6 @@ cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtens
 }
 
 }  // namespace
-
-#ifdef FA2_TRACE
-extern "C" int fa2_trace_read_fwd(long long* out, int n) {
-  return static_cast<int>(cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * n));
-}
-#endif
 
 cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                        const CUtensorMap& tv, const CUtensorMap& to, float* lse,

@@ -89,19 +89,17 @@ __device__ __forceinline__ void issue_tileT_x_tile(uint32_t elected, uint32_t d_
 // element (reduction row r, column c) at byte (c / 8) * 2048 + r * 16 + (c % 8) * 2, i.e. core
 // matrices of 8 rows x 16 bytes, consecutive along the reduction rows (128 bytes apart) and
 // 2048 bytes apart along the columns.
-#ifndef FA2_NS_LBO
-#define FA2_NS_LBO 128   /* stride between core matrices along the reduction (K) index */
-#define FA2_NS_SBO 2048  /* stride between core matrices along the M index */
-#endif
+constexpr uint32_t kPiecesT_Lbo = 128;   // stride between core matrices along the reduction (K) index
+constexpr uint32_t kPiecesT_Sbo = 2048;  // stride between core matrices along the M index
 template <int D, bool BF16>
 __device__ __forceinline__ void issue_piecesT_x_tile(uint32_t elected, uint32_t d_tmem,
                                                      uint32_t a_addr, uint32_t b_addr,
                                                      uint32_t accumulate) {
   using T = Tile<D>;
   constexpr uint32_t idesc = make_idesc(128, D, BF16, true, true);
-  constexpr uint32_t a_hi = desc_hi_word(FA2_NS_SBO, 0u);  // no swizzle
+  constexpr uint32_t a_hi = desc_hi_word(kPiecesT_Sbo, 0u);  // no swizzle
   constexpr uint32_t b_hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
-  const uint32_t a_lo = desc_lo_word(a_addr, FA2_NS_LBO), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
+  const uint32_t a_lo = desc_lo_word(a_addr, kPiecesT_Lbo), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
 #pragma unroll
   for (int k = 0; k < 8; ++k)
     if (elected)
@@ -114,19 +112,17 @@ __device__ __forceinline__ void issue_piecesT_x_tile(uint32_t elected, uint32_t 
 // is the M index and its columns are the reduction index (K-major, unswizzled: core matrices of
 // 8 rows x 16 bytes, 128 bytes apart along M and 2048 bytes apart along the reduction index);
 // B a staged [128, D] tile (MN-major).
-#ifndef FA2_NSK_LBO
-#define FA2_NSK_LBO 2048  /* stride between core matrices along the reduction (K) index */
-#define FA2_NSK_SBO 128   /* stride between core matrices along the M index */
-#endif
+constexpr uint32_t kPieces_Lbo = 2048;  // stride between core matrices along the reduction (K) index
+constexpr uint32_t kPieces_Sbo = 128;   // stride between core matrices along the M index
 template <int D, bool BF16>
 __device__ __forceinline__ void issue_pieces_x_tile(uint32_t elected, uint32_t d_tmem,
                                                     uint32_t a_addr, uint32_t b_addr,
                                                     uint32_t accumulate) {
   using T = Tile<D>;
   constexpr uint32_t idesc = make_idesc(128, D, BF16, false, true);
-  constexpr uint32_t a_hi = desc_hi_word(FA2_NSK_SBO, 0u);  // no swizzle
+  constexpr uint32_t a_hi = desc_hi_word(kPieces_Sbo, 0u);  // no swizzle
   constexpr uint32_t b_hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
-  const uint32_t a_lo = desc_lo_word(a_addr, FA2_NSK_LBO), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
+  const uint32_t a_lo = desc_lo_word(a_addr, kPieces_Lbo), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
 #pragma unroll
   for (int k = 0; k < 8; ++k)
     if (elected)

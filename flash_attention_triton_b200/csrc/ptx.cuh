@@ -85,37 +85,6 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, co
 }
 
 // ----------------------------------------------------------------------------------------
-// Timeline tracing for pipeline tuning.  Compiled out unless the library is built with
-// -DFA2_TRACE; then FA2_TRACE_EVENT(cond, slot) stores clock64() of the calling thread in a
-// per-translation-unit buffer that a fa2_trace_read_* entry point copies out.
-// ----------------------------------------------------------------------------------------
-#ifdef FA2_TRACE
-constexpr int kTraceSlots = 32768;
-static __device__ long long g_trace[kTraceSlots];
-#define FA2_TRACE_EVENT(cond, slot)                                   \
-  do {                                                                \
-    if ((cond) && (slot) < fa2::kTraceSlots) fa2::g_trace[(slot)] = clock64(); \
-  } while (0)
-// Same, storing the nanosecond globaltimer (to relate cycles to wall time).
-#define FA2_TRACE_TIME(cond, slot)                                    \
-  do {                                                                \
-    if ((cond) && (slot) < fa2::kTraceSlots) {                        \
-      long long t_;                                                   \
-      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));          \
-      fa2::g_trace[(slot)] = t_;                                      \
-    }                                                                 \
-  } while (0)
-#else
-#define FA2_TRACE_TIME(cond, slot) \
-  do {                             \
-  } while (0)
-
-#define FA2_TRACE_EVENT(cond, slot) \
-  do {                              \
-  } while (0)
-#endif
-
-// ----------------------------------------------------------------------------------------
 // Proxy fences and named barriers
 // ----------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -39,6 +39,7 @@ def naive_attention(
     dout: torch.Tensor | None = None,
     softmax_scale: float | None = None,
     dtype: torch.dtype = torch.float64,
+    device: str | torch.device = "cpu",
 ) -> dict[str, torch.Tensor]:
     """Causal attention by its definition, with analytic gradients.
 
@@ -46,14 +47,17 @@ def naive_attention(
     pass tensors already rounded to the kernel's 16-bit dtype to isolate kernel error).  ``k``
     and ``v`` may have a different number of rows than ``q``; the mask ``row >= col`` is then
     aligned at the top left, as in the reference's kernels (``_triton_kernels_v2.py:139-147``).
-    Returns ``o, lse`` and, when ``dout`` is given, ``dq, dk, dv, delta``.
+    Returns ``o, lse`` and, when ``dout`` is given, ``dq, dk, dv, delta``.  ``device`` is where
+    the plain torch arithmetic of this definition runs (the CPU unless a test asks for the
+    full-size configurations, whose N x N fp64 matrices per head are evaluated with the same
+    torch operations on the GPU; results are returned on that device).
     Formula: ``tests/test_flash_attention_2.py:289-294`` of the reference; backward is the
     chain rule the reference's kernel implements (``_triton_kernels_v2.py:312-343``).
     """
-    qf, kf, vf = (t.detach().to("cpu", dtype) for t in (q, k, v))
+    qf, kf, vf = (t.detach().to(device, dtype) for t in (q, k, v))
     n, d = qf.shape[-2], qf.shape[-1]
     scale = softmax_scale or 1.0 / math.sqrt(d)
-    mask = torch.ones(n, kf.shape[-2], dtype=torch.bool).tril()
+    mask = torch.ones(n, kf.shape[-2], dtype=torch.bool, device=device).tril()
     s = (qf @ kf.transpose(-1, -2)) * scale
     s = s.masked_fill(~mask, float("-inf"))
     lse = torch.logsumexp(s, dim=-1)
@@ -61,7 +65,7 @@ def naive_attention(
     o = p @ vf
     out = {"o": o, "lse": lse}
     if dout is not None:
-        dof = dout.detach().to("cpu", dtype)
+        dof = dout.detach().to(device, dtype)
         delta = (o * dof).sum(-1)
         dv = p.transpose(-1, -2) @ dof
         dp = dof @ vf.transpose(-1, -2)
@@ -70,7 +74,7 @@ def naive_attention(
     return out
 
 
-def naive_attention_per_head(q, k, v, dout, softmax_scale=None, dtype=torch.float32):
+def naive_attention_per_head(q, k, v, dout, softmax_scale=None, dtype=torch.float32, device="cpu"):
     """Same as :func:`naive_attention` but looping over (batch, head) to bound memory
     (the score matrix is N^2 per head).  Returns tensors in ``dtype``."""
     b, h = q.shape[:2]
@@ -80,7 +84,7 @@ def naive_attention_per_head(q, k, v, dout, softmax_scale=None, dtype=torch.floa
         for hi in range(h):
             r = naive_attention(
                 q[bi : bi + 1, hi : hi + 1], k[bi : bi + 1, hi : hi + 1], v[bi : bi + 1, hi : hi + 1],
-                dout[bi : bi + 1, hi : hi + 1], softmax_scale, dtype,
+                dout[bi : bi + 1, hi : hi + 1], softmax_scale, dtype, device,
             )
             for key in keys:
                 acc[key].append(r[key])

@@ -30,8 +30,8 @@ def pytest_collection_modifyitems(config, items):
 
 
 def make_inputs(shape, dtype, seed=0, qk_mul=1.0):
-    """Seeded inputs as BASELINE configs describe them: q, k, v, dO iid N(0,1) drawn in fp32 on a
-    CPU generator in that order, q and k optionally scaled, then rounded to ``dtype``."""
+    """Seeded inputs: q, k, v, dO iid N(0,1) drawn in fp32 on a CPU generator in that order,
+    q and k optionally scaled (a peaked softmax), then rounded to ``dtype``."""
     g = torch.Generator(device="cpu").manual_seed(seed)
     q, k, v, do = (torch.randn(*shape, generator=g) for _ in range(4))
     q, k = q * qk_mul, k * qk_mul
@@ -40,3 +40,26 @@ def make_inputs(shape, dtype, seed=0, qk_mul=1.0):
 
 def default_scale(d):
     return 1.0 / math.sqrt(d)
+
+
+# --------------------------------------------------------------------------- tolerances
+#: max-abs bounds against the fp64 oracle on the same 16-bit inputs
+BASE_TOL = {torch.float16: 5e-3, torch.bfloat16: 2e-2}
+#: explicit mantissa bits of the output formats
+MANTISSA_BITS = {torch.float16: 10, torch.bfloat16: 7}
+
+
+def elementwise_tolerance(dtype, ref):
+    """Per-element error bound: the stated max-abs bound (5e-3 for fp16, 2e-2 for bf16), or one
+    unit in the last place of the element's OWN oracle value where that is larger (an output
+    rounded to 16 bits cannot be closer than half an ulp to the exact value, so a flat bound is
+    unattainable for |x| >= 8 in fp16 and |x| >= 4 in bf16)."""
+    mag = ref.detach().double().abs().clamp_min(2.0**-60)
+    ulp = torch.exp2(torch.floor(torch.log2(mag)) - MANTISSA_BITS[dtype])
+    return ulp.clamp_min(BASE_TOL[dtype])
+
+
+def error_stats(got, ref):
+    """max-abs and rms error of ``got`` against ``ref`` (both taken to fp64 on ref's device)."""
+    d = got.detach().to(ref.device, torch.float64) - ref.detach().double()
+    return d.abs().max().item(), d.pow(2).mean().sqrt().item()

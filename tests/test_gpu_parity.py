@@ -2,12 +2,16 @@
 vectors, and size-independent properties.  Everything here calls the C ABI (directly through
 ctypes, or through the Python surface that wraps it).
 
-Tolerances (stated by the task for this operator, measured on the FINAL tensors against the
-fp64 closed-form oracle evaluated on the same 16-bit inputs):
+Tolerances, measured on the FINAL tensors against the fp64 closed-form oracle evaluated on the
+same 16-bit inputs:
     fp16 outputs: max-abs <= 5e-3          bf16 outputs: max-abs <= 2e-2
-and never worse than the reference's own error.  Where |x| reaches tens (the peaked-softmax
-configuration) one fp16 ulp exceeds 5e-3, so there the bound is 2 ulps of the largest value,
-the same rule tests/test_oracle.py applies to the reference's own outputs.
+applied element by element, with one escape: an element whose own oracle value is so large that
+one unit in its last place exceeds the bound may be off by that one ulp (|x| >= 8 in fp16,
+|x| >= 4 in bf16; conftest.elementwise_tolerance).  The third criterion, "never worse than the
+reference's own error", is what binds where not even the reference's arithmetic meets the flat
+bound (peaked softmax, gradients of tens accumulated from 16-bit dS tiles): there the error is
+compared with that of the restatement of the reference's kernels (oracle.reference_tiled,
+pinned to their outputs by tests/test_oracle.py) on the same inputs.
 """
 
 from __future__ import annotations
@@ -18,7 +22,7 @@ import numpy as np
 import pytest
 import torch
 
-from conftest import GOLDEN_DIR, make_inputs
+from conftest import BASE_TOL, GOLDEN_DIR, elementwise_tolerance, error_stats, make_inputs
 from flash_attention_triton_b200 import (
     KernelsConfigV2,
     _lib,
@@ -26,17 +30,10 @@ from flash_attention_triton_b200 import (
     flash_attention_v2_custom,
     shard_slab,
 )
-from oracle.attention_oracle import naive_attention, naive_attention_per_head
+from oracle.attention_oracle import naive_attention, naive_attention_per_head, reference_tiled
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-
-
-def tol_for(dtype, ref):
-    base = 5e-3 if dtype == torch.float16 else 2e-2
-    eps = 2.0**-10 if dtype == torch.float16 else 2.0**-7
-    mag = float(ref.abs().max())
-    return max(base, 2 * eps * 2 ** math.floor(math.log2(max(mag, 1e-30))))
 
 
 def run_api(q, k, v, do, scale, det, dev=DEV):
@@ -57,11 +54,39 @@ def run_api_no_sync(q, k, v, do, scale, det, dev=DEV):
 
 
 def check_against(ref, got, dtype, keys=("o", "dq", "dk", "dv")):
+    """Every element within max(5e-3 | 2e-2, one ulp of its own oracle value)."""
+    problems = []
     for key in keys:
-        g = got[key].detach().cpu().double()
+        want = ref[key].double()
+        g = got[key].detach().to(want.device, torch.float64)
         assert not torch.isnan(g).any(), key
-        err = (g - ref[key].double()).abs().max().item()
-        assert err <= tol_for(dtype, ref[key]), f"{key}: max-abs error {err:.3e}"
+        err = (g - want).abs()
+        excess = (err - elementwise_tolerance(dtype, want)).max().item()
+        if excess > 0:
+            problems.append(f"{key}: max-abs error {err.max().item():.3e}, {excess:.3e} over the bound")
+    assert not problems, "; ".join(problems)
+
+
+def check_not_worse_than_reference(q, k, v, do, scale, got, ref, dtype, keys=("dq", "dk", "dv"),
+                                   block=128):
+    """"Never worse than the reference's own error": the reference computes in fp16 whatever the
+    input dtype (flash_attention_2.py:316,339,379) and returns the input dtype, so its side is
+    reference_tiled on the inputs cast to fp16 with the outputs rounded to ``dtype``.  Ours
+    must have the same error level (rms within 25 %) and a maximum within 2x of the reference's
+    (a maximum over 1e5..1e7 elements is a tail value quantised in ulps), or meet the flat bound."""
+    d = q.shape[-1]
+    theirs = reference_tiled(q.half().numpy(), k.half().numpy(), v.half().numpy(), do.half().numpy(),
+                             scale or 1.0 / math.sqrt(d), block, block, block)
+    report = {}
+    for key in keys:
+        want = ref[key].double().cpu()
+        t = torch.from_numpy(theirs[key].astype(np.float32)).to(dtype).double()
+        e_ref, rms_ref = error_stats(t, want)
+        e_ours, rms_ours = error_stats(got[key].cpu(), want)
+        report[key] = {"max_ours": e_ours, "max_ref": e_ref, "rms_ours": rms_ours, "rms_ref": rms_ref}
+        assert rms_ours <= 1.25 * rms_ref + 1e-5, f"{key}: rms ours {rms_ours:.3e}, reference {rms_ref:.3e}"
+        assert e_ours <= max(BASE_TOL[dtype], 2.0 * e_ref), f"{key}: ours {e_ours:.3e}, reference {e_ref:.3e}"
+    return report
 
 
 # --------------------------------------------------------------------------- oracle parity
@@ -392,8 +417,8 @@ def test_matches_reference_kernel_outputs(path):
     for key in ("o", "dq", "dk", "dv"):
         ours = got[key].cpu().double()
         theirs = torch.from_numpy(z[key].astype(np.float64))
-        tol = tol_for(torch.float16, ref[key])
-        assert (ours - theirs).abs().max() <= 2 * tol, key
+        tol = elementwise_tolerance(torch.float16, ref[key])
+        assert ((ours - theirs).abs() - 2 * tol).max() <= 0, key
         e_ours = (ours - ref[key]).abs().max().item()
         e_ref = (theirs - ref[key]).abs().max().item()
         assert e_ours <= 1.5 * e_ref + 1e-3, f"{key}: ours {e_ours:.3e} vs reference {e_ref:.3e}"

@@ -14,6 +14,8 @@ import pytest
 import torch
 import torch.nn.functional as F
 
+from conftest import elementwise_tolerance
+
 from flash_attention_triton_b200 import (KernelsConfigV2, _lib, flash_attention_v2,
                                          flash_attention_v2_custom, init_to_zero_v2)
 
@@ -74,10 +76,16 @@ def test_agrees_with_torch_sdpa_including_gradients(name):
     theirs = forward_backward(
         lambda a, b, c: F.scaled_dot_product_attention(a, b, c, is_causal=True, scale=scale), q, k, v, do)
     assert torch.allclose(ours[0], theirs[0], atol=ATOL, rtol=RTOL), "output"
-    # the kernels compute in fp16 (the reference's dtype policy for fp32 inputs): gradients of
-    # magnitude up to ~10 carry fp16 rounding of P and dS
-    for label, a, b in zip(("dq", "dk", "dv"), ours[1:], theirs[1:]):
-        assert torch.allclose(a, b, atol=2e-2, rtol=2e-2), (label, (a - b).abs().max().item())
+    # Gradients: the kernels compute in fp16 (the reference's dtype policy for fp32 inputs,
+    # flash_attention_2.py:316), so the comparison that isolates kernel error is against torch's
+    # fp32 attention on the SAME fp16-rounded inputs, element by element within
+    # max(5e-3, one fp16 ulp of the element's own value).
+    q16, k16, v16, do16 = (t.half().float() for t in (q, k, v, do))
+    exact = forward_backward(
+        lambda a, b, c: F.scaled_dot_product_attention(a, b, c, is_causal=True, scale=scale), q16, k16, v16, do16)
+    for label, a, b in zip(("dq", "dk", "dv"), ours[1:], exact[1:]):
+        over = ((a - b).abs().double() - elementwise_tolerance(torch.float16, b)).max().item()
+        assert over <= 0, (label, (a - b).abs().max().item(), over)
     assert _lib.device_status() == 0
 
 
