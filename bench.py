@@ -281,7 +281,7 @@ def main():
     lse = torch.empty(lb, lh, n, device=dev, dtype=torch.float32)
     rowstats = torch.empty(lib.fa2_rowstats_bytes(lb, lh, n) // 4, device=dev, dtype=torch.float32)
     wsb = lib.fa2_bwd_workspace_bytes(lb, lh, n, d, mode)
-    ws = torch.empty(max(wsb // 4, 4), device=dev, dtype=torch.float32)
+    ws = torch.empty(max(wsb, 256), device=dev, dtype=torch.uint8)
     stream = torch.cuda.current_stream().cuda_stream
 
     def k_fwd():
@@ -295,7 +295,7 @@ def main():
     def k_bwd():
         _lib.check("fa2_bwd", lib.fa2_bwd(
             q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), rowstats.data_ptr(),
-            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr() if wsb else None,
+            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr() if wsb else None, wsb,
             lb, lh, n, d, code, scale, mode, stream))
 
     def step():

@@ -22,7 +22,7 @@ SYMBOLS = [
     ("fa2_fwd", c_int, [c_void_p] * 5 + [c_int] * 5 + [c_float, c_void_p]),
     ("fa2_bwd_preprocess", c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p]),
     ("fa2_rowstats_bytes", c_size_t, [c_int] * 3),
-    ("fa2_bwd", c_int, [c_void_p] * 9 + [c_int] * 5 + [c_float, c_int, c_void_p]),
+    ("fa2_bwd", c_int, [c_void_p] * 9 + [c_size_t] + [c_int] * 5 + [c_float, c_int, c_void_p]),
     ("fa2_bwd_workspace_bytes", c_size_t, [c_int] * 5),
     ("fa2_set_spill_budget", c_size_t, [c_size_t]),
     ("fa2_device_status", c_int, [ctypes.POINTER(c_int)]),
@@ -32,7 +32,7 @@ SYMBOLS = [
     ("fa2_fwd_strided", c_int, [c_void_p] * 5 + [c_int] * 6 + [c_float, c_void_p, c_void_p]),
     ("fa2_bwd_preprocess_strided", c_int, [c_void_p] * 4 + [c_int] * 5 + [c_void_p, c_void_p]),
     ("fa2_bwd_strided", c_int,
-     [c_void_p] * 9 + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p]),
+     [c_void_p] * 9 + [c_size_t] + [c_int] * 6 + [c_float, c_int, c_void_p, c_void_p]),
 ]
 
 

@@ -44,6 +44,17 @@ def _dtype_code(dtype: torch.dtype) -> int:
     raise AssertionError("Supports only fp16 and bf16 compute dtypes")
 
 
+def _check_status_if_asked(fn: str) -> None:
+    """Kernels that give up on a bounded wait leave their outputs unwritten and only set the
+    device status word; reading it synchronises the device, so it is not read by default.
+    ``FA2_B200_CHECK_STATUS=1`` makes every forward / backward call read it and raise
+    ``Fa2Error`` (``FA2_ERR_DEVICE_STATUS``) when it is non-zero."""
+    if os.environ.get("FA2_B200_CHECK_STATUS") == "1":
+        word = _lib.device_status()
+        if word:
+            raise _lib.Fa2Error(fn, -7, f"{_lib.lib().fa2_strerror(-7).decode()} (status {word:#x})")
+
+
 def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
@@ -98,22 +109,29 @@ def _flash_attention_forward(
                 float(softmax_scale), _lib.stride_array(q, k, v, output), _stream(q),
             ),
         )
+        _check_status_if_asked("fa2_fwd_strided")
     return output, lse, softmax_scale
 
 
 #: dQ strategies of the C library (the ``deterministic`` argument of ``fa2_bwd``)
 _MODE_ATOMIC, _MODE_RECOMPUTE, _MODE_SPILL = 0, 1, 2
-#: the spill mode keeps 32 KiB per tile pair; beyond this much per head (the library's default
-#: scratch bound: one head must fit) it is not used
-_SPILL_MAX_BYTES_PER_HEAD = 8 << 30
+_MODE_NAMES = {"atomic": _MODE_ATOMIC, "recompute": _MODE_RECOMPUTE, "spill": _MODE_SPILL}
+#: the spill mode keeps 32 KiB per tile pair of a head in scratch; when one head's tiles exceed
+#: this much (N above ~45 k) the recompute mode, which needs no scratch, takes over
+_SCRATCH_MAX_BYTES_PER_HEAD = 2 << 30
+
+
+def _scratch_bytes_per_head(seqlen_q: int, headdim: int) -> int:
+    tiles = (seqlen_q + 127) // 128
+    return tiles * (tiles + 1) // 2 * 32768 * (2 if headdim > 128 else 1)
 
 
 def _backward_mode(deterministic: bool, headdim: int, seqlen_q: int) -> int:
     """Which dQ strategy serves ``deterministic``.
 
     ``True`` must give the same bits whatever the batch / head partitioning, so the choice
-    depends on the sequence length only: the spill mode (fastest deterministic one) unless its
-    scratch per head is too large, then the recompute mode.  ``False`` (the reference's
+    depends on the sequence length only: the spill mode (fastest deterministic one) unless one
+    head's scratch is too large, then the recompute mode.  ``False`` (the reference's
     default, atomics there) means "fastest": the spill mode where it beats the atomic kernel
     (head dims above 64), the atomic kernel elsewhere.  ``FA2_B200_BWD_MODE`` = ``atomic`` /
     ``recompute`` / ``spill`` overrides both (for experiments).
@@ -122,12 +140,39 @@ def _backward_mode(deterministic: bool, headdim: int, seqlen_q: int) -> int:
         return _MODE_SPILL
     forced = os.environ.get("FA2_B200_BWD_MODE")
     if forced:
-        return {"atomic": _MODE_ATOMIC, "recompute": _MODE_RECOMPUTE, "spill": _MODE_SPILL}[forced]
-    tiles = (seqlen_q + 127) // 128
-    spill_ok = tiles * (tiles + 1) // 2 * 32768 <= _SPILL_MAX_BYTES_PER_HEAD
+        return _MODE_NAMES[forced]
+    scratch_ok = _scratch_bytes_per_head(seqlen_q, headdim) <= _SCRATCH_MAX_BYTES_PER_HEAD
     if deterministic:
-        return _MODE_SPILL if spill_ok else _MODE_RECOMPUTE
-    return _MODE_SPILL if spill_ok and headdim > 64 else _MODE_ATOMIC
+        return _MODE_SPILL if scratch_ok else _MODE_RECOMPUTE
+    return _MODE_SPILL if scratch_ok and headdim > 64 else _MODE_ATOMIC
+
+
+def _allocate_workspace(lib, device, batch, nheads, seqlen_q, headdim, mode):
+    """The workspace of a backward mode, and the mode that will run.
+
+    The scratch of the spill mode is a convenience, not a need (the reference's backward is
+    O(N) in memory, ``flash_attention_2.py:195-196``): when the recommended size cannot be had,
+    an eighth of it is tried (more chunks, a few per cent slower), then one head's worth, and
+    when even that fails the recompute backward, which needs no scratch and gives the same dK,
+    dV and a dQ that differs in the last bit at most, runs instead.  Head dims above 128 have no
+    scratch-free backward: there the out-of-memory error propagates.
+    """
+    want = lib.fa2_bwd_workspace_bytes(batch, nheads, seqlen_q, headdim, mode)
+    if not want:
+        return None, 0, mode
+    sizes = [want]
+    if mode == _MODE_SPILL:
+        one_head = _scratch_bytes_per_head(seqlen_q, headdim)
+        sizes += [n for n in (want // 8 // one_head * one_head, one_head) if one_head <= n < sizes[-1]]
+    for nbytes in sizes:
+        try:
+            return torch.empty(nbytes, device=device, dtype=torch.uint8), nbytes, mode
+        except torch.cuda.OutOfMemoryError:
+            continue
+    if mode == _MODE_SPILL and headdim <= 128:
+        return None, 0, _MODE_RECOMPUTE
+    raise torch.cuda.OutOfMemoryError(
+        f"no memory for the backward workspace ({sizes[-1]} bytes at least)")
 
 
 def _flash_attention_backward(
@@ -146,9 +191,9 @@ def _flash_attention_backward(
     """Launch ``fa2_bwd_preprocess`` and ``fa2_bwd``.
 
     Counterpart of ``_flash_attention_backward`` (reference lines 147-277).  The workspace
-    behind ``dq_accum`` depends on the dQ strategy (:func:`_backward_mode`): an fp32 accumulator
-    for the atomic kernel, the dS scratch for the spill mode, nothing for the recompute mode;
-    the two deterministic modes write dQ once, already rounded.
+    depends on the dQ strategy (:func:`_backward_mode`): an fp32 accumulator for the atomic
+    kernel, the dS scratch for the spill mode, nothing for the recompute mode; the
+    deterministic modes write dQ once, already rounded.
     """
     batch, nheads, seqlen_q, headdim = q.shape
     seqlen_k = k.shape[2]
@@ -177,20 +222,19 @@ def _flash_attention_backward(
             ),
         )
         mode = _backward_mode(bool(deterministic), headdim, seqlen_q)
-        ws_bytes = lib.fa2_bwd_workspace_bytes(batch, nheads, seqlen_q, headdim, mode)
-        dq_accum = (
-            torch.empty(ws_bytes // 4, device=q.device, dtype=torch.float32) if ws_bytes else None
-        )
+        workspace, ws_bytes, mode = _allocate_workspace(
+            lib, q.device, batch, nheads, seqlen_q, headdim, mode)
         _lib.check(
             "fa2_bwd_strided",
             lib.fa2_bwd_strided(
                 q.data_ptr(), k.data_ptr(), v.data_ptr(), d_output.data_ptr(), rowstats.data_ptr(),
                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                dq_accum.data_ptr() if dq_accum is not None else None,
+                workspace.data_ptr() if workspace is not None else None, ws_bytes,
                 batch, nheads, seqlen_q, seqlen_k, headdim, code, float(softmax_scale),
                 mode, _lib.stride_array(q, k, v, d_output, dq, dk, dv), _stream(q),
             ),
         )
+        _check_status_if_asked("fa2_bwd_strided")
 
 
 # ------------------------------------------------------------------ autograd integration

@@ -157,24 +157,27 @@ int check_shape(int B, int H, int N, int D, int dtype) {
   return FA2_OK;
 }
 
-// Spill mode (deterministic == 2): the dS scratch is bounded by working through the problem in
-// chunks of whole batch entries, or of head ranges of one batch entry when a single entry is
-// already too large.  The split never changes a bit of the results (every (batch, head)
-// problem is independent); it depends on H and N only.
-std::atomic<long long> g_spill_budget{8ll << 30};
-struct SpillPlan {
-  int nb, nh;  // batch entries and heads per chunk
-};
-// Scratch bytes per (batch, head) problem: one 32 KiB dS tile per (KV tile, Q tile) pair, and
-// a P tile as well for head dims above 128.
-long long spill_bytes_per_head(int N, int D) {
-  return dstile_pairs(N, N) * 32768 * (D > 128 ? 2 : 1);
+// Scratch of the spilling backward modes: one 32 KiB dS tile per (KV tile, Q tile) pair of a
+// head, and a P tile as well for head dims above 128.
+long long spill_bytes_per_head(int N, int Nk, int D) {
+  return dstile_pairs(N, Nk) * 32768 * (D > 128 ? 2 : 1);
 }
-SpillPlan spill_plan(int B, int H, int N, int D) {
-  const long long per_head = spill_bytes_per_head(N, D);
-  const long long heads_fit = std::max<long long>(1, g_spill_budget.load() / per_head);
+// What fa2_bwd_workspace_bytes recommends at most (fa2_set_spill_budget); a workspace of any size
+// that holds one head is accepted by fa2_bwd.
+std::atomic<long long> g_spill_budget{8ll << 30};
+
+// Spill mode (and head dims above 128, which have no other backward): the problem is worked
+// through in chunks of whole batch entries, or of head ranges of one batch entry, that fit the
+// workspace.  The split never changes a bit of the results (every (batch, head) problem is
+// independent).
+struct SpillPlan {
+  int nb, nh;  // batch entries and heads per chunk; nb == 0: not even one head fits
+};
+SpillPlan spill_plan(int B, int H, long long per_head, long long bytes) {
+  const long long heads_fit = bytes / per_head;
+  if (heads_fit < 1) return SpillPlan{0, 0};
   if (heads_fit >= H)
-    return SpillPlan{static_cast<int>(std::min<long long>(B, std::max<long long>(1, heads_fit / H))), H};
+    return SpillPlan{static_cast<int>(std::min<long long>(B, heads_fit / H)), H};
   const long long nchunks = (H + heads_fit - 1) / heads_fit;
   return SpillPlan{1, static_cast<int>((H + nchunks - 1) / nchunks)};
 }
@@ -205,7 +208,7 @@ const char* fa2_strerror(int code) {
     case FA2_ERR_DRIVER: return "cuTensorMapEncodeTiled is unavailable or rejected the tensor";
     case FA2_ERR_SCALE: return "softmax scale must be finite and > 0";
     case FA2_ERR_WORKSPACE:
-      return "this backward mode needs the dq_accum workspace (fa2_bwd_workspace_bytes)";
+      return "this backward mode needs a workspace of at least its minimum size (fa2_bwd_workspace_bytes)";
     case FA2_ERR_STRIDE:
       return "strides must be positive multiples of 8 elements (16 bytes), row stride >= D";
     case FA2_ERR_TOO_LARGE: return "problem exceeds the built-in scratch (B*H*ceil(N/128) > 4096)";
@@ -249,7 +252,7 @@ int fa2_fwd(const void* q, const void* k, const void* v, void* o, float* lse, in
 size_t fa2_rowstats_bytes(int B, int H, int N) {
   if (B <= 0 || H <= 0 || N <= 0) return 0;
   const size_t ntiles = (static_cast<size_t>(N) + 127) / 128;
-  return static_cast<size_t>(B) * H * ntiles * 256 * sizeof(float);
+  return static_cast<size_t>(B) * H * ntiles * (256 + 1) * sizeof(float);  // two vectors + one word per tile
 }
 
 int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse, float* rowstats,
@@ -258,6 +261,7 @@ int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse
   if (!o || !dout || !lse || !rowstats) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
   if (!aligned16(o) || !aligned16(dout) || !aligned16(rowstats)) return FA2_ERR_MISALIGNED;
+  if (static_cast<long long>(B) * H * ((N + 127) / 128) > 0x7fffffffll) return FA2_ERR_SHAPE;  // one block per tile
   Strides so, sdo;
   if (int e = get_strides(strides, 0, B, H, N, D, &so)) return e;
   if (int e = get_strides(strides, 1, B, H, N, D, &sdo)) return e;
@@ -275,40 +279,88 @@ int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float*
 
 size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
   if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
-  if (deterministic == 2 || D > 128) {  // 16-bit [128 x 128] tiles per (KV tile, Q tile) pair of a chunk
-    const SpillPlan plan = spill_plan(B, H, N, D);
-    return static_cast<size_t>(plan.nb) * plan.nh * static_cast<size_t>(spill_bytes_per_head(N, D));
+  const long long BH = static_cast<long long>(B) * H;
+  if (deterministic == 2 || D > 128) {
+    // 16-bit [128 x 128] tiles of whole heads: all of them when the budget allows (one chunk is
+    // fastest), else what the chunk plan uses of the budget, never less than one head
+    const long long per_head = spill_bytes_per_head(N, N, D);
+    const SpillPlan plan = spill_plan(B, H, per_head, std::max(per_head, g_spill_budget.load()));
+    return static_cast<size_t>(plan.nb) * plan.nh * static_cast<size_t>(per_head);
   }
   if (deterministic == 1) return 0;
   const size_t ntiles = (static_cast<size_t>(N) + 127) / 128;
-  return static_cast<size_t>(B) * H * ntiles * 128 * padded_head_dim(D) * sizeof(float);
+  return static_cast<size_t>(BH) * ntiles * 128 * padded_head_dim(D) * sizeof(float);
 }
 
-int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dout,
-                    const float* rowstats, void* dq, void* dk, void* dv, float* dq_accum, int B,
-                    int H, int N, int Nk, int D, int dtype, float scale, int deterministic,
-                    const long long* strides, fa2_stream_t stream) {
+// fa2_bwd_strided with the two parts of the preprocess output given separately, so that a chunk of
+// a larger problem (see the chunk loop below) can point into the arrays of the whole problem.
+static int bwd_strided(const void* q, const void* k, const void* v, const void* dout,
+                       const float* rowstats_ptr, const unsigned* tile_amax, void* dq, void* dk,
+                       void* dv, void* workspace, size_t workspace_bytes, int B, int H, int N, int Nk,
+                       int D, int dtype, float scale, int deterministic, const long long* strides,
+                       fa2_stream_t stream) {
+  const float* rowstats = rowstats_ptr;
   if (!q || !k || !v || !dout || !rowstats || !dq || !dk || !dv) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
   if (Nk < 1 || Nk > N) return FA2_ERR_SHAPE;
+  if (deterministic < 0 || deterministic > 2) return FA2_ERR_SHAPE;
   // Head dims above 128 have one backward (scores kernel + three consumer kernels over two
-  // scratch tensors); it is deterministic and serves every value of `deterministic`.
+  // scratch tensors, in chunks); it is deterministic and serves every value of `deterministic`.
   if (D > 128) deterministic = 2;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(dout) || !aligned16(dq) ||
       !aligned16(dk) || !aligned16(dv) || !aligned16(rowstats))
     return FA2_ERR_MISALIGNED;
   if (!std::isfinite(scale) || !(scale > 0.f)) return FA2_ERR_SCALE;
-  if (deterministic < 0 || deterministic > 2) return FA2_ERR_SHAPE;
-  if (deterministic != 1 && !dq_accum) return FA2_ERR_WORKSPACE;
-  if (deterministic != 1 && !aligned16(dq_accum)) return FA2_ERR_MISALIGNED;
+  if (static_cast<long long>(B) * H * ((N + 127) / 128) > 0x7fffffffll) return FA2_ERR_SHAPE;  // one CTA per tile
+  if (deterministic != 1 && !workspace) return FA2_ERR_WORKSPACE;
+  if (deterministic != 1 && (reinterpret_cast<uintptr_t>(workspace) & 255u)) return FA2_ERR_MISALIGNED;
+  // The workspace must hold what the mode needs at least; what lies beyond is used when it
+  // helps (more scratch slots, larger chunks) and never written otherwise.
+  const long long BH = static_cast<long long>(B) * H;
+  const long long per_head = spill_bytes_per_head(N, Nk, D);
+  const long long ws = static_cast<long long>(std::min<size_t>(workspace_bytes, size_t(1) << 62));
+  if (deterministic == 0 && workspace_bytes < fa2_bwd_workspace_bytes(B, H, N, D, 0))
+    return FA2_ERR_WORKSPACE;
+  if (deterministic == 2 && ws < per_head) return FA2_ERR_WORKSPACE;
   const int rows_of[7] = {N, Nk, Nk, N, N, Nk, Nk};  // q, k, v, dout, dq, dk, dv
+  long long st_all[21];
   for (int idx = 0; idx < 7; ++idx) {
-    Strides unused;
-    if (int e = get_strides(strides, idx, B, H, rows_of[idx], D, &unused)) return e;
+    Strides t;
+    if (int e = get_strides(strides, idx, B, H, rows_of[idx], D, &t)) return e;
+    st_all[3 * idx] = t.b, st_all[3 * idx + 1] = t.h, st_all[3 * idx + 2] = t.n;
   }
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if (deterministic == 2) {
+    const SpillPlan plan = spill_plan(B, H, per_head, ws);
+    if (plan.nb < B || plan.nh < H) {
+      // more than one chunk: the same call on sub-ranges, one after the other on the stream
+      // (they share the scratch), with the caller's strides spelled out
+      const void* in[4] = {q, k, v, dout};
+      void* out[3] = {dq, dk, dv};
+      const size_t stats_per_head = static_cast<size_t>((N + 127) / 128) * 256;
+      for (int b0 = 0; b0 < B; b0 += plan.nb)
+        for (int h0 = 0; h0 < H; h0 += plan.nh) {
+          const int nb = std::min(plan.nb, B - b0), nh = std::min(plan.nh, H - h0);
+          auto at = [&](const void* p, int idx) {
+            return static_cast<const char*>(p) + 2 * (b0 * st_all[3 * idx] + h0 * st_all[3 * idx + 1]);
+          };
+          const int e = bwd_strided(
+              at(in[0], 0), at(in[1], 1), at(in[2], 2), at(in[3], 3),
+              rowstats + (static_cast<size_t>(b0) * H + h0) * stats_per_head,
+              tile_amax + (static_cast<size_t>(b0) * H + h0) * ((N + 127) / 128),
+              const_cast<char*>(at(out[0], 4)), const_cast<char*>(at(out[1], 5)),
+              const_cast<char*>(at(out[2], 6)), workspace, workspace_bytes, nb, nh, N, Nk, D, dtype,
+              scale, 2, st_all, stream);
+          if (e) return e;
+        }
+      return FA2_OK;
+    }
+    if (BH * dstile_pairs(N, Nk) >= (1ll << 31)) return FA2_ERR_SHAPE;
+  }
+
   CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
   if (int e = make_map_of(&tq, q, strides, 0, dtype, B, H, N, D, 128)) return e;
   if (int e = make_map_of(&tk, k, strides, 1, dtype, B, H, Nk, D, 128)) return e;
@@ -316,81 +368,66 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
   if (int e = make_map_of(&tdo, dout, strides, 3, dtype, B, H, N, D, 128)) return e;
   if (int e = make_map_of(&tdk, dk, strides, 5, dtype, B, H, Nk, D, 32)) return e;
   if (int e = make_map_of(&tdv, dv, strides, 6, dtype, B, H, Nk, D, 32)) return e;
-  Strides sdq;
-  if (int e = get_strides(strides, 4, B, H, N, D, &sdq)) return e;
+  const Strides sdq{st_all[12], st_all[13], st_all[14]};
   const AttnShape s = make_shape(B, H, N, Nk, D, dtype, scale);
-  if (deterministic == 1) {
+  const RowStats rs{rowstats, tile_amax};
+  if (deterministic != 0)
     if (int e = make_map(&tdq, dq, dtype, B, H, N, D, sdq, 32)) return e;
+
+  if (deterministic == 1) {
     cudaError_t ce =
-        launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, nullptr, 0, d->status, st);
+        launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rs, nullptr, 0, d->status, st);
     if (ce != cudaSuccess) return static_cast<int>(ce);
-    return static_cast<int>(launch_bwd_dq(s, tq, tk, tv, tdo, tdq, rowstats, d->status, st));
+    return static_cast<int>(launch_bwd_dq(s, tq, tk, tv, tdo, tdq, rs, d->status, st));
   }
   if (deterministic == 2) {
-    const SpillPlan plan = spill_plan(B, H, N, D);
-    if (plan.nb < B || plan.nh < H) {
-      // more than one chunk: the same call on sub-ranges, one after the other on the stream
-      // (they share the scratch), with the caller's strides spelled out
-      const void* in[4] = {q, k, v, dout};
-      void* out[3] = {dq, dk, dv};
-      long long st_all[21];
-      const int rows_of2[7] = {N, Nk, Nk, N, N, Nk, Nk};
-      for (int idx = 0; idx < 7; ++idx) {
-        Strides t;
-        if (int e = get_strides(strides, idx, B, H, rows_of2[idx], D, &t)) return e;
-        st_all[3 * idx] = t.b, st_all[3 * idx + 1] = t.h, st_all[3 * idx + 2] = t.n;
-      }
-      const size_t stats_per_head = fa2_rowstats_bytes(1, 1, N) / sizeof(float);
-      for (int b0 = 0; b0 < B; b0 += plan.nb)
-        for (int h0 = 0; h0 < H; h0 += plan.nh) {
-          const int nb = std::min(plan.nb, B - b0), nh = std::min(plan.nh, H - h0);
-          auto at = [&](const void* p, int idx) {
-            return static_cast<const char*>(p) + 2 * (b0 * st_all[3 * idx] + h0 * st_all[3 * idx + 1]);
-          };
-          const int e = fa2_bwd_strided(
-              at(in[0], 0), at(in[1], 1), at(in[2], 2), at(in[3], 3),
-              rowstats + (static_cast<size_t>(b0) * H + h0) * stats_per_head,
-              const_cast<char*>(at(out[0], 4)), const_cast<char*>(at(out[1], 5)),
-              const_cast<char*>(at(out[2], 6)), dq_accum, nb, nh, N, Nk, D, dtype, scale, 2, st_all,
-              stream);
-          if (e) return e;
-        }
-      return FA2_OK;
-    }
-    // dS scratch: one 32 KiB tile per (KV tile, Q tile) pair
-    const long long pairs = static_cast<long long>(B) * H * dstile_pairs(N, Nk);
-    if (pairs >= (1ll << 31)) return FA2_ERR_SHAPE;
-    if (int e = make_map(&tdq, dq, dtype, B, H, N, D, sdq, 32)) return e;
+    float* scratch = static_cast<float*>(workspace);
     if (D > 128) {
       // P tiles first, dS tiles behind them
-      char* p_scratch = reinterpret_cast<char*>(dq_accum);
+      const long long pairs = BH * dstile_pairs(N, Nk);
+      char* p_scratch = static_cast<char*>(workspace);
       char* ds_scratch = p_scratch + static_cast<size_t>(pairs) * 32768;
-      cudaError_t ce = launch_bwd_scores_wide(s, tq, tk, tv, tdo, rowstats, p_scratch, ds_scratch,
+      cudaError_t ce = launch_bwd_scores_wide(s, tq, tk, tv, tdo, rs, p_scratch, ds_scratch,
                                               d->status, st);
       if (ce != cudaSuccess) return static_cast<int>(ce);
-      if ((ce = launch_bwd_consume(s, 0, p_scratch, tdo, tdv, d->status, st)) != cudaSuccess)
+      if ((ce = launch_bwd_consume(s, 0, p_scratch, tdo, tdv, rs, d->status, st)) != cudaSuccess)
         return static_cast<int>(ce);
-      if ((ce = launch_bwd_consume(s, 1, ds_scratch, tq, tdk, d->status, st)) != cudaSuccess)
+      if ((ce = launch_bwd_consume(s, 1, ds_scratch, tq, tdk, rs, d->status, st)) != cudaSuccess)
         return static_cast<int>(ce);
-      return static_cast<int>(launch_bwd_consume(s, 2, ds_scratch, tk, tdq, d->status, st));
+      return static_cast<int>(launch_bwd_consume(s, 2, ds_scratch, tk, tdq, rs, d->status, st));
     }
     cudaError_t ce =
-        launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum, 2, d->status, st);
+        launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rs, scratch, 2, d->status, st);
     if (ce != cudaSuccess) return static_cast<int>(ce);
-    return static_cast<int>(launch_bwd_consume(s, 2, dq_accum, tk, tdq, d->status, st));
+    return static_cast<int>(launch_bwd_consume(s, 2, scratch, tk, tdq, rs, d->status, st));
   }
+  float* dq_accum = static_cast<float*>(workspace);
   cudaError_t ce = cudaMemsetAsync(dq_accum, 0, fa2_bwd_workspace_bytes(B, H, N, D, 0), st);
   if (ce != cudaSuccess) return static_cast<int>(ce);
-  ce = launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rowstats, dq_accum, 1, d->status, st);
+  ce = launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rs, dq_accum, 1, d->status, st);
   if (ce != cudaSuccess) return static_cast<int>(ce);
   return static_cast<int>(launch_dq_convert(s, dq_accum, dq, sdq, st));
 }
 
+int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dout,
+                    const float* rowstats, void* dq, void* dk, void* dv, void* workspace,
+                    size_t workspace_bytes, int B, int H, int N, int Nk, int D, int dtype,
+                    float scale, int deterministic, const long long* strides,
+                    fa2_stream_t stream) {
+  if (!rowstats) return FA2_ERR_NULL_POINTER;
+  if (int e = check_shape(B, H, N, D, dtype)) return e;
+  // the per-tile maxima of |dout| follow the last tile of the row statistics (fa2_bwd_preprocess)
+  const unsigned* tile_amax = reinterpret_cast<const unsigned*>(
+      rowstats + static_cast<size_t>(B) * H * ((N + 127) / 128) * 256);
+  return bwd_strided(q, k, v, dout, rowstats, tile_amax, dq, dk, dv, workspace, workspace_bytes, B,
+                     H, N, Nk, D, dtype, scale, deterministic, strides, stream);
+}
+
 int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const float* rowstats,
-            void* dq, void* dk, void* dv, float* dq_accum, int B, int H, int N, int D, int dtype,
-            float scale, int deterministic, fa2_stream_t stream) {
-  return fa2_bwd_strided(q, k, v, dout, rowstats, dq, dk, dv, dq_accum, B, H, N, N, D, dtype,
-                         scale, deterministic, nullptr, stream);
+            void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes, int B, int H,
+            int N, int D, int dtype, float scale, int deterministic, fa2_stream_t stream) {
+  return fa2_bwd_strided(q, k, v, dout, rowstats, dq, dk, dv, workspace, workspace_bytes, B, H, N,
+                         N, D, dtype, scale, deterministic, nullptr, stream);
 }
 
 size_t fa2_set_spill_budget(size_t bytes) {
@@ -441,8 +478,8 @@ namespace fa2 {
 // Row statistics (-lse*log2e, -delta) of up to kStaticRowstatTiles Q tiles live here instead
 // of in a caller buffer.  In HOST code this name is only a handle for the runtime: the real
 // device address comes from cudaGetSymbolAddress, once per device, below.
-constexpr int kStaticRowstatTiles = 4096;  // 4096 tiles x 256 floats = 4 MiB per GPU
-static __device__ __align__(256) float g_static_rowstats[kStaticRowstatTiles * 256];
+constexpr int kStaticRowstatTiles = 4096;  // 4096 tiles x 257 words = 4.02 MiB per GPU
+static __device__ __align__(256) float g_static_rowstats[kStaticRowstatTiles * (256 + 1)];
 
 namespace {
 struct StaticScratch {
@@ -490,6 +527,6 @@ extern "C" int fa2_bwd_static_scratch(const void* q, const void* k, const void* 
   // Every element of the part of the array that the kernels read is rewritten by the
   // preprocess launch (padding rows included), so nothing has to be cleared first.
   if (int e = fa2_bwd_preprocess(o, dout, lse, rowstats, B, H, N, D, dtype, stream)) return e;
-  return fa2_bwd(q, k, v, dout, rowstats, dq, dk, dv, nullptr, B, H, N, D, dtype, scale,
+  return fa2_bwd(q, k, v, dout, rowstats, dq, dk, dv, nullptr, 0, B, H, N, D, dtype, scale,
                  /*deterministic=*/1, stream);
 }

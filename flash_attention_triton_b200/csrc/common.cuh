@@ -62,8 +62,44 @@ struct Strides {
   long long b, h, n;
 };
 
+// What the backward preprocess leaves for the backward kernels: the tile-blocked row statistics
+// and, one word per 128-row tile, the largest |dout| of the tile (16-bit pattern, sign cleared),
+// both indexed from the first (batch, head) problem of the launch.
+struct RowStats {
+  const float* stats;         // [B*H][T][2][128]
+  const unsigned* tile_amax;  // [B*H][T]
+};
+
 // Smallest instantiated head dim that holds `d` columns.
 inline int padded_head_dim(int d) { return d <= 32 ? 32 : (d <= 64 ? 64 : (d <= 128 ? 128 : 256)); }
+
+// Order in which the causal kernels take their (head, tile) work items.  A tile's work shrinks
+// with its rank (rank 0 is the tile that meets the most tiles of the other kind), so for an even
+// finish the long items must start first; but the items of one head share its tensors through
+// the L2 cache, so they must also run close together.  Heads are therefore taken in groups of
+// `group` whose tensors fit a share of the L2 cache together, and inside a group every head's
+// rank-0 item comes first, then every head's rank-1 item, and so on.  Against the plain
+// head-by-head order this removes most of the causal tail (the last head's longest item no
+// longer starts last): the fewer heads a launch has, the more it gains.
+struct HeadTile {
+  int bh;    // flattened (batch, head) index
+  int rank;  // 0 = the heaviest tile of the head
+};
+__host__ __device__ __forceinline__ HeadTile grouped_order(long long id, int num_bh, int tiles,
+                                                           int group) {
+  const long long per_group = static_cast<long long>(group) * tiles;
+  const int g0 = static_cast<int>(id / per_group) * group;
+  const int n = num_bh - g0 < group ? num_bh - g0 : group;  // heads of this group
+  const int local = static_cast<int>(id - (id / per_group) * per_group);
+  return HeadTile{g0 + local % n, local / n};
+}
+// Heads per group: q, dout (or o) and k, v of the group's heads in 64 MiB of the 126 MiB L2.
+inline int heads_per_group(const AttnShape& s) {
+  const long long per_head = (2ll * s.N + 2ll * s.Nk) * s.D * 2;
+  const long long g = (64ll << 20) / per_head;
+  const long long bh = static_cast<long long>(s.B) * s.H;
+  return static_cast<int>(g < 1 ? 1 : (g > bh ? bh : g));
+}
 
 // Per-launch context of the forward kernel.  It runs one CTA per SM; each CTA fetches work
 // items (pairs of Q tiles) from `work_counter` until none are left, so tensor memory is
@@ -91,7 +127,9 @@ cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensor
                        const CUtensorMap& tv, const CUtensorMap& to, float* lse,
                        const LaunchCtx& ctx, cudaStream_t stream);
 
-// rowstats[bh][t][0][r] = -lse * log2(e) (-inf for padded rows), rowstats[bh][t][1][r] = -delta.
+// rowstats[bh][t][0][r] = -lse * log2(e) (-inf for padded rows), rowstats[bh][t][1][r] = -delta;
+// behind the last tile, one 32-bit word per tile: the largest |dout| of the tile's rows as its
+// 16-bit pattern with the sign cleared.
 cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strides& so,
                                   const void* dout, const Strides& sdo, const float* lse,
                                   float* rowstats, cudaStream_t stream);
@@ -104,7 +142,7 @@ cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strid
 cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                             const CUtensorMap& tv, const CUtensorMap& tdo,
                             const CUtensorMap& tdk, const CUtensorMap& tdv,
-                            const float* rowstats, float* dq_accum, int mode, int* status,
+                            const RowStats& rowstats, float* dq_accum, int mode, int* status,
                             cudaStream_t stream);
 
 // Head dim 256: P^T and dS^T of every (KV tile, Q tile) pair as 16-bit piece-major tiles into two
@@ -112,7 +150,7 @@ cudaError_t launch_bwd_dkdv(const AttnShape& s, const CUtensorMap& tq, const CUt
 // give dV, dK and dQ.
 cudaError_t launch_bwd_scores_wide(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                                    const CUtensorMap& tv, const CUtensorMap& tdo,
-                                   const float* rowstats, void* p_scratch, void* ds_scratch,
+                                   const RowStats& rowstats, void* p_scratch, void* ds_scratch,
                                    int* status, cudaStream_t stream);
 
 // One output tile per CTA from spilled 16-bit score-gradient / probability tiles, one product
@@ -121,8 +159,8 @@ cudaError_t launch_bwd_scores_wide(const AttnShape& s, const CUtensorMap& tq, co
 //   form 0: dV(jt) = sum_i P(jt, i)^T dO_i   (scratch = P tiles,  tb = dO, tout = dV)  head dim 256
 //   form 1: dK(jt) = sum_i dS(jt, i)^T Q_i   (scratch = dS tiles, tb = Q,  tout = dK)  head dim 256
 cudaError_t launch_bwd_consume(const AttnShape& s, int form, const void* scratch,
-                               const CUtensorMap& tb, const CUtensorMap& tout, int* status,
-                               cudaStream_t stream);
+                               const CUtensorMap& tb, const CUtensorMap& tout, const RowStats& rowstats,
+                               int* status, cudaStream_t stream);
 
 // (KV tile, Q tile) pairs of one head: KV tile t < nktiles meets Q tiles t .. ntiles-1.
 inline long long dstile_pairs(int N, int Nk) {
@@ -133,7 +171,7 @@ inline long long dstile_pairs(int N, int Nk) {
 // dQ per Q tile, ascending KV order (deterministic path).
 cudaError_t launch_bwd_dq(const AttnShape& s, const CUtensorMap& tq, const CUtensorMap& tk,
                           const CUtensorMap& tv, const CUtensorMap& tdo, const CUtensorMap& tdq,
-                          const float* rowstats, int* status, cudaStream_t stream);
+                          const RowStats& rowstats, int* status, cudaStream_t stream);
 
 // dq = convert(dq_accum) (non-deterministic path).
 cudaError_t launch_dq_convert(const AttnShape& s, const float* dq_accum, void* dq,

@@ -2,7 +2,8 @@
 //
 //   bwd_preprocess_kernel  delta[row] = sum_d float(o[row,d]) * float(dout[row,d])
 //       replaces _backward_preprocess_do_o_dot (_triton_kernels_v2.py:532-608 of the
-//       reference).  Algorithmic traffic per row: 2 * D * 2 bytes read + 4 bytes written.
+//       reference).  Algorithmic traffic per row: 2 * D * 2 bytes read + 4 bytes (lse) read +
+//       8 bytes written.
 //   dq_convert_kernel      dq = 16-bit(dq_accum), the single fp32 -> 16-bit rounding the
 //       reference performs with dq.copy_(dq_accum) (flash_attention_2.py:277).
 #include "common.cuh"
@@ -41,61 +42,85 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
 }
 
 constexpr int kPreThreads = 256;
-constexpr int kPreRowsInFlight = 2;  // independent rows per thread group, for loads in flight
+constexpr int kPreMaxInFlight = 8;  // rows a thread group has in flight at once (2 x 16 bytes each)
 constexpr float kLog2e = 1.4426950408889634f;
 
-// A group of D/8 adjacent lanes owns one row: each lane reads one 16-byte piece of o and of
-// dout, multiplies, and the group reduces with shuffles in a fixed order (deterministic).
+// One block per 128-row tile of one (batch, head).  A group of D/8 adjacent lanes owns a row: each
+// lane reads one 16-byte piece of o and of dout, multiplies, and the group reduces with shuffles
+// in a fixed order (deterministic).  The block's 256 threads cover 2048 / D rows per pass and a
+// thread issues the loads of up to kPreMaxInFlight passes (16 independent 16-byte loads) before it
+// uses the first one, which is what keeps enough bytes in flight to fill the HBM pipe.
 // D is the padded head dim; a row in memory has d8 <= D/8 pieces and the lanes beyond it
-// contribute zeros.
-// Rows are enumerated over the padded range [BH][T*128] so that the padding of rowstats is
-// written too (-lse2 = -inf makes every probability of a padded row exactly 0 downstream).
-// Both vectors are stored NEGATED so the consumers can use them as FMA / ADD addends directly.
+// contribute zeros.  Rows beyond N are written too: -lse2 = -inf makes every probability of a
+// padded row exactly 0 downstream.  Both vectors are stored NEGATED so the consumers can use them
+// as FMA / ADD addends directly.  The block also leaves the largest |dout| of its rows, as the
+// 16-bit pattern with the sign cleared, in tile_amax[tile] (see head_dscale in bwd_roles.cuh).
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kPreThreads)
     bwd_preprocess_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dout,
-                          const float* __restrict__ lse, float* __restrict__ rowstats, int N,
-                          int npad, long long padded_rows, int d8, int H, Strides so,
-                          Strides sdo) {
+                          const float* __restrict__ lse, float* __restrict__ rowstats,
+                          unsigned* __restrict__ tile_amax, int N, int ntiles, int d8, int H,
+                          Strides so, Strides sdo) {
   constexpr int kLanesPerRow = D / 8;
-  constexpr int kRowsPerBlockPass = kPreThreads / kLanesPerRow;
+  constexpr int kRowsPerPass = kPreThreads / kLanesPerRow;  // 64, 32, 16 or 8
+  constexpr int kPasses = 128 / kRowsPerPass;               // 2, 4, 8 or 16
+  constexpr int kBatch = kPasses < kPreMaxInFlight ? kPasses : kPreMaxInFlight;
+  __shared__ unsigned warp_max[kPreThreads / 32];
+  const long long tile = blockIdx.x;  // = bh * ntiles + t
+  const long long bh = tile / ntiles;
+  const int t = static_cast<int>(tile - bh * ntiles);
+  const long long bb = bh / H, hh = bh - bb * H;
   const int sub = threadIdx.x % kLanesPerRow;
-  const long long row_in_pass = threadIdx.x / kLanesPerRow;
-  const long long base_row =
-      static_cast<long long>(blockIdx.x) * (kRowsPerBlockPass * kPreRowsInFlight) + row_in_pass;
-  uint4 a[kPreRowsInFlight], b[kPreRowsInFlight];
-  long long src_row[kPreRowsInFlight];
+  const int row_in_pass = threadIdx.x / kLanesPerRow;
+  // strides are in 16-byte units (the host divides the element strides by 8)
+  const uint4* o_head = o + bb * so.b + hh * so.h;
+  const uint4* do_head = dout + bb * sdo.b + hh * sdo.h;
+  float* out = rowstats + tile * 256;
+  unsigned amax2 = 0;  // two running maxima of 15-bit magnitudes, one per 16-bit half
 #pragma unroll
-  for (int i = 0; i < kPreRowsInFlight; ++i) {
-    const long long prow = base_row + static_cast<long long>(i) * kRowsPerBlockPass;
-    const long long bh = prow / npad;
-    const int rr = static_cast<int>(prow - bh * npad);
-    src_row[i] = (prow < padded_rows && rr < N) ? bh * N + rr : -1;
-    if (src_row[i] >= 0 && sub < d8) {
-      // strides are in 16-byte units (the host divides the element strides by 8)
-      const long long bb = bh / H, hh = bh - bb * H;
-      a[i] = ld_stream(o + bb * so.b + hh * so.h + rr * so.n + sub);
-      b[i] = ld_stream(dout + bb * sdo.b + hh * sdo.h + rr * sdo.n + sub);
-    } else {
-      a[i] = make_uint4(0, 0, 0, 0);
-      b[i] = make_uint4(0, 0, 0, 0);
+  for (int p0 = 0; p0 < kPasses; p0 += kBatch) {
+    uint4 a[kBatch], b[kBatch];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int r = (p0 + i) * kRowsPerPass + row_in_pass;  // row inside the tile
+      const long long row = static_cast<long long>(t) * 128 + r;
+      if (row < N && sub < d8) {
+        a[i] = ld_stream(o_head + row * so.n + sub);
+        b[i] = ld_stream(do_head + row * sdo.n + sub);
+      } else {
+        a[i] = make_uint4(0, 0, 0, 0);
+        b[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      float acc = dot8<BF16>(a[i], b[i]);
+#pragma unroll
+      for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
+        acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      amax2 = __vmaxu2(amax2, b[i].x & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].y & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].z & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].w & 0x7fff7fffu);
+      const int r = (p0 + i) * kRowsPerPass + row_in_pass;
+      if (sub == 0) {
+        const long long row = static_cast<long long>(t) * 128 + r;
+        const bool valid = row < N;
+        out[r] = valid ? -lse[bh * N + row] * kLog2e : -INFINITY;
+        out[128 + r] = valid ? -acc : 0.f;
+      }
     }
   }
+  // largest magnitude of the block: halves, warp, block (a NaN or inf pattern wins, which
+  // head_dscale treats as "do not scale")
+  unsigned m = max(amax2 & 0xffffu, amax2 >> 16);
+  m = __reduce_max_sync(0xffffffffu, m);
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
 #pragma unroll
-  for (int i = 0; i < kPreRowsInFlight; ++i) {
-    float acc = dot8<BF16>(a[i], b[i]);
-#pragma unroll
-    for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
-      acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    const long long prow = base_row + static_cast<long long>(i) * kRowsPerBlockPass;
-    if (sub == 0 && prow < padded_rows) {
-      // prow = (bh*T + t)*128 + r  ->  rowstats[(bh*T + t)*256 + {0,128} + r]
-      const long long tile = prow >> 7;
-      const int r = static_cast<int>(prow & 127);
-      const bool valid = src_row[i] >= 0;
-      rowstats[tile * 256 + r] = valid ? -lse[src_row[i]] * kLog2e : -INFINITY;
-      rowstats[tile * 256 + 128 + r] = valid ? -acc : 0.f;
-    }
+    for (int i = 1; i < kPreThreads / 32; ++i) m = max(m, warp_max[i]);
+    tile_amax[tile] = m;
   }
 }
 
@@ -139,13 +164,11 @@ cudaError_t launch_pre_t(const AttnShape& s, const void* o, const Strides& so, c
                          const Strides& sdo, const float* lse, float* rowstats,
                          cudaStream_t stream) {
   const int ntiles = (s.N + 127) / 128;
-  const int npad = ntiles * 128;
-  const long long padded_rows = static_cast<long long>(s.B) * s.H * npad;
-  constexpr int kRowsPerBlock = kPreThreads / (D / 8) * kPreRowsInFlight;
-  const long long blocks = (padded_rows + kRowsPerBlock - 1) / kRowsPerBlock;
-  bwd_preprocess_kernel<D, BF16><<<static_cast<unsigned>(blocks), kPreThreads, 0, stream>>>(
-      static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, s.N, npad,
-      padded_rows, s.Dg / 8, s.H, in_vec8(so), in_vec8(sdo));
+  const long long tiles = static_cast<long long>(s.B) * s.H * ntiles;
+  unsigned* tile_amax = reinterpret_cast<unsigned*>(rowstats + tiles * 256);  // behind the last tile
+  bwd_preprocess_kernel<D, BF16><<<static_cast<unsigned>(tiles), kPreThreads, 0, stream>>>(
+      static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, tile_amax, s.N,
+      ntiles, s.Dg / 8, s.H, in_vec8(so), in_vec8(sdo));
   return cudaGetLastError();
 }
 

@@ -85,7 +85,7 @@ template <int D, bool BF16>
 __global__ void __launch_bounds__(kFwdThreads, 1)
     fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap to,
-               float* __restrict__ lse, int N, int Nk, int num_bh, int num_heads,
+               float* __restrict__ lse, int N, int Nk, int num_bh, int num_heads, int group,
                float scale_log2, int* status, unsigned int* work_counter) {
   // Head dim 256 ("wide") runs on the staging and tensor-memory plan of head dim 128 with ONE
   // Q tile per work item: the two Q slots hold the two 128-column halves of that tile, K and V
@@ -167,9 +167,10 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
     const int item = *work_slot;
     if (item >= total_items) break;
     if (*abort_flag) continue;  // keep drawing so that the counter is left at zero
-    const int bh = item / npairs;
+    const HeadTile ht = grouped_order(item, num_bh, npairs, group);
+    const int bh = ht.bh;
     const HeadCoord hc{bh % num_heads, bh / num_heads};
-    const int pair = npairs - 1 - (item - bh * npairs);  // heavy pairs of a head first
+    const int pair = npairs - 1 - ht.rank;  // the last pair of Q tiles meets the most KV tiles
     const int qt0 = WIDE ? pair : 2 * pair, qt1 = qt0 + 1;
     const bool has1 = !WIDE && qt1 < ntiles;
     // KV tiles of Q tile i: 0 .. min(i, last KV tile)  (N = query rows, Nk <= N = key rows)
@@ -405,7 +406,7 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
           t.y = ex2(t.y);
         }
         acc[c & 3] = __fadd2_rn(acc[c & 3], t);
-        pk[c] = pack2<BF16>(t.x, t.y);
+        pk[c] = pack2<kInterBF16<BF16>>(t.x, t.y);
       }
       if (j > 0 && !pv_waited) {
         // P_i still feeds O_i += P_i(j-1) V_(j-1) until that product has completed
@@ -492,7 +493,8 @@ cudaError_t launch_fwd_t(const AttnShape& s, const CUtensorMap& tq, const CUtens
   const unsigned grid = static_cast<unsigned>(items < ctx.num_sms ? items : ctx.num_sms);
   const float scale_log2 = s.scale * 1.4426950408889634f;
   kern<<<grid, kFwdThreads, C::kSmemBytes, stream>>>(tq, tk, tv, to, lse, s.N, s.Nk, s.B * s.H, s.H,
-                                                     scale_log2, ctx.status, ctx.work_counter);
+                                                     heads_per_group(s), scale_log2, ctx.status,
+                                                     ctx.work_counter);
   return cudaGetLastError();
 }
 

@@ -6,6 +6,10 @@
 // constant upper word of its shared-memory descriptors once and derives the eight per-step
 // descriptors with one 32-bit add each (the start-address field is the only part that moves,
 // and it cannot carry out of its 14 bits for addresses below 256 KiB).
+//
+// Operand types: tiles staged from the caller's tensors (Q, K, V, dO) and the operands the kernels
+// produce themselves (P and dS, in tensor memory, in shared memory or spilled to global memory)
+// all have the tensors' dtype (kInterBF16 in ptx.cuh).
 #pragma once
 #include "common.cuh"
 #include "ptx.cuh"
@@ -53,7 +57,7 @@ __device__ __forceinline__ void issue_tmem_x_tile(uint32_t elected, uint32_t d_t
                                                   uint32_t a_tmem, uint32_t a_col_half,
                                                   uint32_t b_addr, uint32_t accumulate) {
   using T = Tile<D>;
-  constexpr uint32_t idesc = make_idesc(128, D, BF16, false, true);
+  constexpr uint32_t idesc = make_idesc_ab(128, D, kInterBF16<BF16>, BF16, false, true);
   constexpr uint32_t hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
   const uint32_t b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
 #pragma unroll
@@ -72,7 +76,7 @@ __device__ __forceinline__ void issue_tileT_x_tile(uint32_t elected, uint32_t d_
                                                    uint32_t a_addr, uint32_t b_addr,
                                                    uint32_t accumulate = 0u) {
   using T = Tile<D>;
-  constexpr uint32_t idesc = make_idesc(128, D, BF16, true, true);
+  constexpr uint32_t idesc = make_idesc_ab(128, D, kInterBF16<BF16>, BF16, true, true);
   constexpr uint32_t a_hi = desc_hi_word(1024, kSwizzle128B);
   constexpr uint32_t b_hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
   const uint32_t a_lo = desc_lo_word(a_addr, 16384), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
@@ -96,7 +100,7 @@ __device__ __forceinline__ void issue_piecesT_x_tile(uint32_t elected, uint32_t 
                                                      uint32_t a_addr, uint32_t b_addr,
                                                      uint32_t accumulate) {
   using T = Tile<D>;
-  constexpr uint32_t idesc = make_idesc(128, D, BF16, true, true);
+  constexpr uint32_t idesc = make_idesc_ab(128, D, kInterBF16<BF16>, BF16, true, true);
   constexpr uint32_t a_hi = desc_hi_word(kPiecesT_Sbo, 0u);  // no swizzle
   constexpr uint32_t b_hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
   const uint32_t a_lo = desc_lo_word(a_addr, kPiecesT_Lbo), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);
@@ -119,7 +123,7 @@ __device__ __forceinline__ void issue_pieces_x_tile(uint32_t elected, uint32_t d
                                                     uint32_t a_addr, uint32_t b_addr,
                                                     uint32_t accumulate) {
   using T = Tile<D>;
-  constexpr uint32_t idesc = make_idesc(128, D, BF16, false, true);
+  constexpr uint32_t idesc = make_idesc_ab(128, D, kInterBF16<BF16>, BF16, false, true);
   constexpr uint32_t a_hi = desc_hi_word(kPieces_Sbo, 0u);  // no swizzle
   constexpr uint32_t b_hi = desc_hi_word(T::kAtomBytes, T::kSwizzleMode);
   const uint32_t a_lo = desc_lo_word(a_addr, kPieces_Lbo), b_lo = desc_lo_word(b_addr, T::kChunkTileBytes);

@@ -279,13 +279,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
 }
 
 // Instruction descriptor for kind::f16 with fp32 accumulation: [4,6) D format (1 = f32),
-// [7,10) A format, [10,13) B format (0 = f16, 1 = bf16), bit 15 / 16 = A / B is MN-major,
-// [17,23) N>>3, [24,29) M>>4.
-__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16, bool a_mn_major,
-                                                  bool b_mn_major) {
-  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
+// [7,10) A format, [10,13) B format (0 = f16, 1 = bf16; the two are independent fields), bit 15 /
+// 16 = A / B is MN-major, [17,23) N>>3, [24,29) M>>4.
+__host__ __device__ constexpr uint32_t make_idesc_ab(int m, int n, bool a_bf16, bool b_bf16,
+                                                     bool a_mn_major, bool b_mn_major) {
+  return (1u << 4) | ((a_bf16 ? 1u : 0u) << 7) | ((b_bf16 ? 1u : 0u) << 10) |
          ((a_mn_major ? 1u : 0u) << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+// Both operands of the tensors' dtype.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16, bool a_mn_major,
+                                                  bool b_mn_major) {
+  return make_idesc_ab(m, n, bf16, bf16, a_mn_major, b_mn_major);
 }
 
 // ----------------------------------------------------------------------------------------
@@ -334,6 +339,14 @@ template <int N>
 __device__ __forceinline__ void reg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
+// Type of the operands the kernels produce themselves (probabilities P, score gradients dS):
+// that of the tensors.  (fp16 P and dS next to bf16 tensors would give bf16 problems the 11
+// significant bits the reference's all-fp16 arithmetic has, flash_attention_2.py:316, but
+// tcgen05.mma.kind::f16 takes an fp16 A operand with a bf16 B operand as an illegal instruction
+// on this part, although the descriptor has one format field per operand.)
+template <bool BF16>
+constexpr bool kInterBF16 = BF16;
+
 // Two fp32 -> one 32-bit word holding two 16-bit values, `lo` in bits [0,16).
 template <bool BF16>
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {

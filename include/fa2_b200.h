@@ -8,7 +8,7 @@
  * [B, H, N].  D is a multiple of 8 between 8 and 256 (32, 64, 128 and 256 are the native tile
  * widths; sizes in between run zero-padded to the next one through TMA out-of-bounds fill, with
  * no extra memory traffic); dtype 0 = fp16, 1 = bf16.  Above D = 128 the backward has a single,
- * deterministic strategy that needs the workspace fa2_bwd_workspace_bytes reports whatever
+ * deterministic strategy that needs a workspace (fa2_bwd_workspace_bytes) whatever
  * `deterministic` says, and fa2_bwd_static_scratch is not available (FA2_ERR_WORKSPACE).
  *
  * Return value: 0 = success; negative = argument / environment error (table below);
@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define FA2_ABI_VERSION 2
+#define FA2_ABI_VERSION 3
 
 #define FA2_DTYPE_FP16 0
 #define FA2_DTYPE_BF16 1
@@ -49,7 +49,7 @@ extern "C" {
 #define FA2_ERR_DEVICE_STATUS (-7)     /* a kernel gave up on a bounded wait */
 #define FA2_ERR_DRIVER (-8)            /* cuTensorMapEncodeTiled unavailable or failed */
 #define FA2_ERR_SCALE (-9)             /* softmax scale not finite or not > 0 */
-#define FA2_ERR_WORKSPACE (-10)        /* dq_accum is NULL although the mode needs a workspace */
+#define FA2_ERR_WORKSPACE (-10)        /* the mode needs a workspace: NULL, or smaller than its minimum */
 #define FA2_ERR_TOO_LARGE (-11)        /* fa2_bwd_static_scratch: B*H*ceil(N/128) > 4096 */
 #define FA2_ERR_STRIDE (-12)           /* a stride is <= 0, not a multiple of 8 elements, or row < D */
 
@@ -92,47 +92,51 @@ size_t fa2_rowstats_bytes(int B, int H, int N);
 
 /*
  * Backward main.  Inputs q,k,v,dout and rowstats (from fa2_bwd_preprocess); outputs
- * dq,dk,dv in the input dtype.
- *   deterministic == 1: dK/dV kernel + a separate dQ kernel that recomputes S and dP; every
- *     output tile has one owner and a fixed accumulation order, so results are bit-identical
- *     across runs, SM counts and (batch, head) partitionings.  dq_accum is not used (may be
- *     NULL).
- *   deterministic == 2 ("spill"): equally deterministic, and the fastest mode at D = 128.  The
- *     dK/dV kernel also writes every 16-bit dS tile to the scratch behind dq_accum
- *     (fa2_bwd_workspace_bytes(.., 2) bytes, bounded by fa2_set_spill_budget) and a second
- *     kernel forms dQ from those tiles with one tensor-core product per tile pair, bound by
- *     reading the scratch from HBM.  Trades memory (quadratic in N per head, chunked) for
- *     time; dK and dV are bit-identical to mode 1, dQ differs from it in the last bit at most
- *     (other polynomial / MUFU assignment of the exponentials).  No counterpart in the
- *     reference.
- *   deterministic == 0: one fused kernel per KV tile adds its dQ contributions into the
- *     fp32 workspace dq_accum with atomic adds (the reference's SEQUENCE_PARALLEL mode,
+ * dq,dk,dv in the input dtype.  dK and dV are the same bits in every mode (every KV tile sums
+ * its Q tiles from the last one down to the diagonal); the modes differ in how dQ is formed and
+ * in the workspace they need (`workspace`, 256-byte aligned, `workspace_bytes` long; the call
+ * never writes beyond it and returns FA2_ERR_WORKSPACE when it is below the mode's minimum).
+ *   deterministic == 1 ("recompute"): dK/dV kernel + a separate dQ kernel that recomputes S and
+ *     dP; every output tile has one owner and a fixed accumulation order, so results are
+ *     bit-identical across runs, SM counts and (batch, head) partitionings.  No workspace
+ *     (memory O(N) like the reference, flash_attention_2.py:195-196).
+ *   deterministic == 2 ("spill"): equally deterministic, and the fastest mode at D = 128 when the
+ *     scratch can be afforded.  The dK/dV kernel also writes every 16-bit dS tile (32 KiB per
+ *     (KV tile, Q tile) pair) to the workspace and a second kernel forms dQ from those tiles with
+ *     one tensor-core product per pair in ascending KV order, bound by reading them back from
+ *     HBM.  Trades memory (quadratic in N per head: 68 MB at N = 8192) for time.  The problem is
+ *     worked through in chunks of whole (batch, head) problems that fit the workspace given, one
+ *     after the other on the stream; one chunk is fastest, the minimum is one head's tiles, and
+ *     the split never changes a bit of the results.  dQ differs from mode 1 in the last bit at
+ *     most (other polynomial / MUFU assignment of the exponentials).  It is the only backward
+ *     for head dims above 128, where it is a scores kernel plus dV, dK and dQ kernels over two
+ *     scratch tensors (64 KiB per tile pair) and serves every value of `deterministic`.  No
+ *     counterpart in the reference.
+ *   deterministic == 0 ("atomic"): one fused kernel per KV tile adds its dQ contributions into
+ *     the fp32 workspace with atomic adds (the reference's SEQUENCE_PARALLEL mode,
  *     _triton_kernels_v2.py:337-339), then a convert pass writes dq, rounding once like
- *     dq.copy_(dq_accum) (flash_attention_2.py:277).  dq_accum must hold
- *     fa2_bwd_workspace_bytes() bytes, 16-byte aligned; this call zeroes it itself.  Its
- *     layout is private (tile-blocked so that every warp-wide atomic is one contiguous
- *     512-byte run).
+ *     dq.copy_(dq_accum) (flash_attention_2.py:277).  The workspace is the fp32 accumulator
+ *     [B*H][ceil(N/128)*128][D padded to 32/64/128]; this call zeroes it itself.  Its layout is
+ *     private (tile-blocked so that every warp-wide atomic is one contiguous 512-byte run).
  */
 int fa2_bwd(const void* q, const void* k, const void* v, const void* dout,
             const float* rowstats,
-            void* dq, void* dk, void* dv, float* dq_accum,
+            void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes,
             int B, int H, int N, int D, int dtype, float scale, int deterministic,
             fa2_stream_t stream);
 
 /*
- * Bytes of workspace fa2_bwd needs behind `dq_accum` for a value of `deterministic`:
- *   0  fp32 dQ accumulator of the atomic mode, [B*H][ceil(N/128)*128][D padded to 32/64/128];
- *   1  none (two-kernel deterministic mode: dQ is recomputed from S and dP);
- *   2  the dS scratch of the spill mode, 32 KiB per (KV tile, Q tile) pair of one chunk.
+ * Bytes of workspace fa2_bwd should be given for a value of `deterministic` (see there): the
+ * exact size for modes 0 and 1 (0 bytes), the recommended size for mode 2: every head's tiles
+ * when fa2_set_spill_budget allows, else what the chunks that fit the budget use, never less
+ * than one head.
  */
 size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic);
 
 /*
- * Upper bound of the spill-mode scratch in bytes (default 8 GiB); returns the previous value.
- * Larger problems run in chunks of batch entries / head ranges that fit, one after the other.
- * The split is a function of (H, N) and this bound only and never changes a bit of the
- * results.  Process-wide; do not change it while calls are in flight on other threads, and
- * query fa2_bwd_workspace_bytes again after changing it.  No counterpart in the reference.
+ * Upper bound of what fa2_bwd_workspace_bytes recommends for mode 2, in bytes (default 8 GiB);
+ * returns the previous value.  fa2_bwd itself never reads it: it works with the
+ * workspace it is given.  Process-wide.  No counterpart in the reference.
  */
 size_t fa2_set_spill_budget(size_t bytes);
 
@@ -151,7 +155,7 @@ size_t fa2_set_spill_budget(size_t bytes);
  * A triple of zeros means "dense"; strides == NULL means every tensor is dense (the plain
  * entry points above are exactly that).  Every stride must be a positive multiple of 8
  * elements (16 bytes) and the row stride at least D, else FA2_ERR_STRIDE; strides of
- * dimensions of size 1 are ignored.  lse, rowstats and dq_accum keep their dense layouts.
+ * dimensions of size 1 are ignored.  lse, rowstats and the workspace keep their own layouts.
  *
  * They also take the number of key rows separately: q, o, dout, dq and lse have N rows, k, v,
  * dk and dv have Nk rows, 1 <= Nk <= N.  The causal mask is aligned at the top left like the
@@ -167,7 +171,7 @@ int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse
                                const long long* strides, fa2_stream_t stream);
 int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dout,
                     const float* rowstats,
-                    void* dq, void* dk, void* dv, float* dq_accum,
+                    void* dq, void* dk, void* dv, void* workspace, size_t workspace_bytes,
                     int B, int H, int N, int Nk, int D, int dtype, float scale,
                     int deterministic, const long long* strides, fa2_stream_t stream);
 

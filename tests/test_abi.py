@@ -38,7 +38,7 @@ def test_binding_table_covers_header():
 
 def test_abi_version_and_error_text():
     lib = _lib.lib()
-    assert lib.fa2_abi_version() == 2
+    assert lib.fa2_abi_version() == 3
     assert lib.fa2_strerror(0) == b"success"
     assert b"multiple of 8" in lib.fa2_strerror(-2)
     assert lib.fa2_strerror(-12345) == b"unknown fa2 error code"
@@ -46,8 +46,8 @@ def test_abi_version_and_error_text():
 
 def test_size_queries():
     lib = _lib.lib()
-    # rowstats: [B*H][ceil(N/128)][2][128] fp32
-    assert lib.fa2_rowstats_bytes(2, 3, 4095) == 2 * 3 * 32 * 256 * 4
+    # rowstats: [B*H][ceil(N/128)][2][128] fp32, then one word per tile (its largest |dout|)
+    assert lib.fa2_rowstats_bytes(2, 3, 4095) == 2 * 3 * 32 * (256 + 1) * 4
     assert lib.fa2_rowstats_bytes(0, 3, 128) == 0
     # dq workspace: fp32 [B*H][ceil(N/128)*128][D], none in deterministic mode
     assert lib.fa2_bwd_workspace_bytes(2, 3, 4095, 32, 0) == 2 * 3 * 4096 * 32 * 4
@@ -84,9 +84,19 @@ def test_backward_argument_errors_need_no_gpu():
     lib = _lib.lib()
     p = [0x1000 * (i + 1) for i in range(8)]
     # non-deterministic mode without a workspace
-    rc = lib.fa2_bwd(*p[:5], p[5], p[6], p[7], None, 1, 1, 128, 64, 0, 0.125, 0, None)
+    rc = lib.fa2_bwd(*p[:5], p[5], p[6], p[7], None, 0, 1, 1, 128, 64, 0, 0.125, 0, None)
     assert rc == -10
-    rc = lib.fa2_bwd(*p[:5], p[5], p[6], None, None, 1, 1, 128, 64, 0, 0.125, 1, None)
+    # a workspace below the mode's minimum is refused before anything is launched: the atomic
+    # accumulator of [1, 1, 128, 64] is 32 KiB, one head's tile of the spill mode 32 KiB
+    rc = lib.fa2_bwd(*p[:5], p[5], p[6], p[7], 0x10000, 1024, 1, 1, 128, 64, 0, 0.125, 0, None)
+    assert rc == -10
+    rc = lib.fa2_bwd(*p[:5], p[5], p[6], p[7], 0x10000, 32767, 1, 1, 128, 64, 0, 0.125, 2, None)
+    assert rc == -10
+    rc = lib.fa2_bwd(*p[:5], p[5], p[6], p[7], 0x10000, 100, 1, 1, 128, 256, 0, 0.125, 1, None)
+    assert rc == -10
+    rc = lib.fa2_bwd(*p[:5], p[5], p[6], p[7], 0x10010, 1 << 20, 1, 1, 128, 64, 0, 0.125, 2, None)
+    assert rc == -4  # workspace not 256-byte aligned
+    rc = lib.fa2_bwd(*p[:5], p[5], p[6], None, None, 0, 1, 1, 128, 64, 0, 0.125, 1, None)
     assert rc == -1
     rc = lib.fa2_bwd_preprocess(p[0], p[1], p[2], None, 1, 1, 128, 64, 0, None)
     assert rc == -1
@@ -148,6 +158,7 @@ def test_spill_scratch_size_follows_the_budget():
         assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == 32 * pairs * 32768
         lib.fa2_set_spill_budget(20 * pairs * 32768)      # 20 heads fit: two chunks of 16
         assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == 16 * pairs * 32768
+        assert lib.fa2_bwd_workspace_bytes(2, 16, 8192, 256, 0) == 8 * 2 * pairs * 32768  # 64 KiB per pair: 10 heads fit, two chunks of 8
         lib.fa2_set_spill_budget(1)                       # never below one head
         assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == pairs * 32768
         assert lib.fa2_set_spill_budget(previous) == 1
@@ -162,9 +173,59 @@ def test_backward_mode_choice_depends_on_the_sequence_length_only(monkeypatch):
     monkeypatch.delenv("FA2_B200_BWD_MODE", raising=False)
     assert api._backward_mode(True, 128, 8192) == api._MODE_SPILL
     assert api._backward_mode(True, 32, 4095) == api._MODE_SPILL
-    assert api._backward_mode(True, 128, 65536) == api._MODE_SPILL       # 4 GiB of dS per head
-    assert api._backward_mode(True, 128, 131072) == api._MODE_RECOMPUTE  # 16 GiB per head
+    assert api._backward_mode(True, 128, 32768) == api._MODE_SPILL       # 1 GiB of dS per head
+    assert api._backward_mode(True, 128, 65536) == api._MODE_RECOMPUTE   # 4 GiB per head
     assert api._backward_mode(False, 128, 8192) == api._MODE_SPILL       # fastest at d = 128
     assert api._backward_mode(False, 64, 8192) == api._MODE_ATOMIC
+    assert api._backward_mode(False, 256, 8192) == api._MODE_SPILL       # the one backward there
     monkeypatch.setenv("FA2_B200_BWD_MODE", "recompute")
     assert api._backward_mode(False, 64, 8192) == api._MODE_RECOMPUTE
+
+
+def test_workspace_allocation_falls_back_when_memory_is_short(monkeypatch):
+    """The recommended scratch, an eighth of it, one head's worth, then the scratch-free
+    recompute backward."""
+    import torch
+
+    from flash_attention_triton_b200 import api
+
+    lib = _lib.lib()
+    head = 2080 * 32768
+    want = lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2)
+    assert want == 64 * head
+    calls, limit = [], [1 << 62]
+
+    def fake_empty(nbytes, device=None, dtype=None):
+        calls.append(nbytes)
+        if nbytes > limit[0]:
+            raise torch.cuda.OutOfMemoryError("no memory")
+        return torch.zeros(1, dtype=torch.uint8)
+
+    monkeypatch.setattr(api.torch, "empty", fake_empty)
+    assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_SPILL)[1:] == (want, api._MODE_SPILL)
+    limit[0] = 1 << 30  # 8 heads fit
+    calls.clear()
+    assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_SPILL)[1:] == (8 * head, api._MODE_SPILL)
+    limit[0] = 100 << 20  # one head (68 MB) fits
+    calls.clear()
+    assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_SPILL)[1:] == (head, api._MODE_SPILL)
+    assert calls == [want, 8 * head, head]
+    # exactly what fa2_bwd accepts as the minimum: refused with one byte less
+    assert lib.fa2_bwd(*([0x1000] * 8), 0x10000, head - 1, 1, 1, 8192, 128, 1, 0.1, 2, None) == -10
+    limit[0] = 1 << 20
+    assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_SPILL) == (None, 0, api._MODE_RECOMPUTE)
+    with pytest.raises(torch.cuda.OutOfMemoryError):  # head dim 256 has no scratch-free backward
+        api._allocate_workspace(lib, "cpu", 2, 16, 8192, 256, api._MODE_SPILL)
+    assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_RECOMPUTE) == (None, 0, 1)
+
+
+def test_static_scratch_refuses_bad_arguments_before_launching():
+    """Everything fa2_bwd would refuse is refused before the preprocess kernel could overwrite the
+    shared array: head dims above 128, a bad scale, misaligned pointers."""
+    lib = _lib.lib()
+    p = [0x1000] * 9
+    assert lib.fa2_bwd_static_scratch(*p, 1, 2, 256, 256, 1, 0.1, None) == -10
+    assert lib.fa2_bwd_static_scratch(*p, 1, 2, 256, 64, 1, 0.0, None) == -9
+    assert lib.fa2_bwd_static_scratch(*p, 1, 2, 256, 64, 1, float("nan"), None) == -9
+    assert lib.fa2_bwd_static_scratch(*([0x1000] * 6 + [0x1008] + [0x1000] * 2), 1, 2, 256, 64, 1, 0.1, None) == -4
+    assert lib.fa2_bwd_static_scratch(*p, 1, 65, 8192, 128, 1, 0.1, None) == -11

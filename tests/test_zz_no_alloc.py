@@ -44,7 +44,7 @@ def _backward_with_workspace(lib, q, k, v, o, do, lse, scale, code):
                                   b, h, n, d, code, st) == 0
     dq, dk, dv = (torch.empty_like(q) for _ in range(3))
     assert lib.fa2_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), rs.data_ptr(),
-                       dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), None,
+                       dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), None, 0,
                        b, h, n, d, code, scale, 1, st) == 0
     return dq, dk, dv
 
