@@ -169,6 +169,36 @@ def cpu_baseline(b, h, n, d, dtype, qk_mul, scale, budget_s=12.0, max_heads=32):
                       f"attention + analytic backward, {el:.1f} s"}
 
 
+def triton_reference(workload, our_ms):
+    """The reference's own Triton kernels on this GPU (informational: the unmodified package from
+    baseline/_ref through its public API, in a child process, after every timed region)."""
+    import subprocess
+
+    cmd = [sys.executable, str(ROOT / "baseline" / "reference_triton_bench.py"), "--workload", workload,
+           "--steps", "3"]
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=420)
+    except Exception as exc:  # noqa: BLE001
+        return {"unavailable": repr(exc)[:200]}
+    recs = []
+    for ln in out.stdout.splitlines():
+        try:
+            recs.append(json.loads(ln))
+        except ValueError:
+            pass
+    if not recs or "unavailable" in recs[0]:
+        return {"unavailable": (recs[0]["unavailable"] if recs else (out.stderr or "no output")[-200:])}
+    res = {"config": WORKLOADS[workload][:4], "note": recs[0].get("note"), "triton": recs[0].get("triton")}
+    for r in recs:
+        key = "deterministic" if r.get("deterministic") else "default"
+        default_err = r.get("tried", {}).get("default", {}).get("error")
+        res[key] = {"fwd_bwd_ms": r.get("fwd_bwd_ms"), "tflops": r.get("fwd_bwd_tflops"),
+                    "fwd_ms": r.get("fwd_ms"), "best_config": r.get("config"),
+                    "default_config_error": default_err,
+                    "ours_over_triton": (r["fwd_bwd_ms"] / our_ms) if r.get("fwd_bwd_ms") else None}
+    return res
+
+
 def run_reference_arm(args, rank, world):
     wl = WORKLOADS[args.workload]
     b, h, n, d, dtype, qk_mul, scale = wl
@@ -232,6 +262,8 @@ def main():
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling legs (c3, c4 split over the GPUs)")
+    ap.add_argument("--no-triton-reference", action="store_true")
     ap.add_argument("--sustain-seconds", type=float, default=1.0,
                     help="extra untimed-for-the-metric run of the same step under the clock sampler")
     args = ap.parse_args()
@@ -276,32 +308,7 @@ def main():
     my_fwd_flops = fwd_flops(lb, lh, n, d)
 
     lib = _lib.lib()
-    q, k, v, do = (t.to(dev) for t in host)
-    o, dq, dk, dv = (torch.empty_like(q) for _ in range(4))
-    lse = torch.empty(lb, lh, n, device=dev, dtype=torch.float32)
-    rowstats = torch.empty(lib.fa2_rowstats_bytes(lb, lh, n) // 4, device=dev, dtype=torch.float32)
-    wsb = lib.fa2_bwd_workspace_bytes(lb, lh, n, d, mode)
-    ws = torch.empty(max(wsb, 256), device=dev, dtype=torch.uint8)
-    stream = torch.cuda.current_stream().cuda_stream
-
-    def k_fwd():
-        _lib.check("fa2_fwd", lib.fa2_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
-                                          lse.data_ptr(), lb, lh, n, d, code, scale, stream))
-
-    def k_pre():
-        _lib.check("fa2_bwd_preprocess", lib.fa2_bwd_preprocess(
-            o.data_ptr(), do.data_ptr(), lse.data_ptr(), rowstats.data_ptr(), lb, lh, n, d, code, stream))
-
-    def k_bwd():
-        _lib.check("fa2_bwd", lib.fa2_bwd(
-            q.data_ptr(), k.data_ptr(), v.data_ptr(), do.data_ptr(), rowstats.data_ptr(),
-            dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), ws.data_ptr() if wsb else None, wsb,
-            lb, lh, n, d, code, scale, mode, stream))
-
-    def step():
-        k_fwd()
-        k_pre()
-        k_bwd()
+    peaks = load_peaks()
 
     def barrier():
         torch.cuda.synchronize()
@@ -309,90 +316,167 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(x):
+    def reduce_over_ranks(x, op):
         if world == 1:
             return x
         t = torch.tensor([x], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=op)
         return float(t.item())
+
+    def max_over_ranks(x):
+        return reduce_over_ranks(x, dist.ReduceOp.MAX if world > 1 else None)
 
     def sum_over_ranks(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
+        return reduce_over_ranks(x, dist.ReduceOp.SUM if world > 1 else None)
 
+    class Problem:
+        """Device-resident buffers of one problem and the three C-ABI calls of a step on them."""
+
+        def __init__(self, tensors, n, d, code, scale, mode):
+            self.q, self.k, self.v, self.do = (t.to(dev) for t in tensors)
+            self.lb, self.lh = self.q.shape[0], self.q.shape[1]
+            self.n, self.d, self.code, self.scale, self.mode = n, d, code, scale, mode
+            self.o, self.dq, self.dk, self.dv = (torch.empty_like(self.q) for _ in range(4))
+            self.lse = torch.empty(self.lb, self.lh, n, device=dev, dtype=torch.float32)
+            self.rowstats = torch.empty(lib.fa2_rowstats_bytes(self.lb, self.lh, n) // 4, device=dev,
+                                        dtype=torch.float32)
+            self.wsb = lib.fa2_bwd_workspace_bytes(self.lb, self.lh, n, d, mode)
+            self.ws = torch.empty(max(self.wsb, 256), device=dev, dtype=torch.uint8)
+            self.stream = torch.cuda.current_stream().cuda_stream
+            self.fwd_flops = fwd_flops(self.lb, self.lh, n, d)
+
+        def fwd(self):
+            _lib.check("fa2_fwd", lib.fa2_fwd(
+                self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.o.data_ptr(),
+                self.lse.data_ptr(), self.lb, self.lh, self.n, self.d, self.code, self.scale, self.stream))
+
+        def pre(self):
+            _lib.check("fa2_bwd_preprocess", lib.fa2_bwd_preprocess(
+                self.o.data_ptr(), self.do.data_ptr(), self.lse.data_ptr(), self.rowstats.data_ptr(),
+                self.lb, self.lh, self.n, self.d, self.code, self.stream))
+
+        def bwd(self):
+            _lib.check("fa2_bwd", lib.fa2_bwd(
+                self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr(), self.do.data_ptr(),
+                self.rowstats.data_ptr(), self.dq.data_ptr(), self.dk.data_ptr(), self.dv.data_ptr(),
+                self.ws.data_ptr() if self.wsb else None, self.wsb, self.lb, self.lh, self.n, self.d,
+                self.code, self.scale, self.mode, self.stream))
+
+        def step(self):
+            self.fwd()
+            self.pre()
+            self.bwd()
+
+        def launches_per_step(self):
+            """Kernels of this library per step: forward, preprocess and the backward-main kernels
+            of the mode (atomic: memset + fused kernel + convert; recompute: dK/dV + dQ; spill:
+            dK/dV + dQ per chunk of the workspace; head dims above 128: scores + three consumers
+            per chunk)."""
+            if self.mode == 2 or self.d > 128:
+                tiles = (self.n + 127) // 128
+                per_head = tiles * (tiles + 1) // 2 * 32768 * (2 if self.d > 128 else 1)
+                chunks = -(-self.lb * self.lh * per_head // max(self.wsb, 1))
+                return 2 + chunks * (4 if self.d > 128 else 2)
+            return 4
+
+        def timed(self, steps, warmup, split=False):
+            """ms per step over `steps` steps after `warmup`, max over ranks, barrier on both sides.
+            With split, every step also records events between its calls (and between the two
+            kernels of the backward call where it has two), and the per-call means are returned:
+            they are parts of the very steps that give the headline."""
+            for _ in range(warmup):
+                self.step()
+            st = _lib.device_status()
+            if st != 0:
+                raise RuntimeError(f"kernel status word {st:#x} after warm-up")
+            two_kernels = self.mode in (1, 2) and self.d <= 128
+            marks = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(steps if split else 0)]
+            for evs in marks:  # an event has no handle before its first record
+                for e in evs:
+                    e.record()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            ev0.record()
+            for i in range(steps):
+                if split:
+                    m = marks[i]
+                    m[0].record()
+                    self.fwd()
+                    m[1].record()
+                    self.pre()
+                    m[2].record()
+                    if two_kernels:
+                        lib.fa2_bwd_mark_between(m[3].cuda_event)
+                    self.bwd()
+                    m[4].record()
+                else:
+                    self.step()
+            ev1.record()
+            torch.cuda.synchronize()
+            barrier()
+            ms = max_over_ranks(ev0.elapsed_time(ev1)) / steps
+            parts = None
+            if split:
+                mean = lambda i, j: sum(m[i].elapsed_time(m[j]) for m in marks) / steps
+                parts = {"fwd": mean(0, 1), "pre": mean(1, 2), "bwd": mean(2, 4)}
+                if two_kernels:
+                    parts["bwd_first"], parts["bwd_second"] = mean(2, 3), mean(3, 4)
+                parts = {key: max_over_ranks(val) for key, val in parts.items()}
+            return ms, parts
+
+    prob = Problem(host, n, d, code, scale, mode)
+    lb, lh = prob.lb, prob.lh
+    q = prob.q
+    my_fwd_flops = prob.fwd_flops
     total_fwd_flops = sum_over_ranks(my_fwd_flops)
 
-    for _ in range(args.warmup):
-        step()
-    st = _lib.device_status()
-    if st != 0:
-        raise RuntimeError(f"kernel status word {st:#x} after warm-up")
-
-    # Kernels of this library per step: forward, preprocess and the backward-main kernels of the
-    # mode (atomic: fused kernel + convert; recompute: dK/dV + dQ; spill: dK/dV + dQ per chunk of
-    # the scratch budget; head dims above 128: scores + three consumers per chunk).
-    if mode == 2 and wsb:
-        tiles = (n + 127) // 128
-        per_head = tiles * (tiles + 1) // 2 * 32768 * (2 if d > 128 else 1)
-        chunks = -(-lb * lh * per_head // wsb)
-        launches_per_step = 2 + chunks * (4 if d > 128 else 2)
-    else:
-        launches_per_step = 4
-
     # ------------------------------------------------------------ timed region (device-resident)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
     with ClockSampler(local_rank) as clocks:
-        ev0.record()
-        for _ in range(args.steps):
-            step()
-        ev1.record()
-        torch.cuda.synchronize()
-    barrier()
-    ms_total = max_over_ranks(ev0.elapsed_time(ev1))
-    ms_per_step = ms_total / args.steps
+        ms_per_step, parts = prob.timed(args.steps, args.warmup, split=True)
     value = 3.5 * total_fwd_flops / (ms_per_step * 1e-3) / 1e12
+    launches_per_step = prob.launches_per_step()
 
-    # ------------------------------------------------------------ per-kernel breakdown
-    def time_kernel(fn):
-        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
-               for _ in range(args.steps)]
-        torch.cuda.synchronize()
-        for a, bb in evs:
-            a.record()
-            fn()
-            bb.record()
-        torch.cuda.synchronize()
-        return sum(a.elapsed_time(bb) for a, bb in evs) / len(evs)
-
-    ms_fwd = max_over_ranks(time_kernel(k_fwd))
-    ms_pre = max_over_ranks(time_kernel(k_pre))
-    ms_bwd = max_over_ranks(time_kernel(k_bwd))
-    peaks = load_peaks()
+    # ------------------------------------------------------------ rooflines, from the same steps
+    ms_fwd, ms_pre, ms_bwd = parts["fwd"], parts["pre"], parts["bwd"]
     bwd_tf = 2.5 * my_fwd_flops / (ms_bwd * 1e-3) / 1e12
     fwd_tf = my_fwd_flops / (ms_fwd * 1e-3) / 1e12
     pre_bytes = 2.0 * lb * lh * n * d * 2 + lb * lh * n * 4 * 3
+    tensor = lambda tf: {"achieved": tf, "frac": tf / peaks["bf16"], "frac_of_sustained": tf / peaks["bf16_sustained"]}
+    hbm = lambda nbytes, ms: {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peaks["hbm"],
+                              "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm"], "ms": ms}
     roofline = {
         "kernel": "bwd_scores_wide_kernel + bwd_consume_kernel x3 (dV, dK, dQ)" if d > 128 else (
             "bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert",
             "bwd_dkdv_kernel + bwd_dq_kernel (S, dP recomputed)",
             "bwd_dkdv_kernel (dS tiles spilled) + bwd_consume_kernel (dQ)")[mode],
-        "bound": "tensor", "achieved": bwd_tf, "peak": peaks["bf16"], "unit": "TFLOP/s",
-        "frac": bwd_tf / peaks["bf16"], "peak_source": f"{peaks['source']} burst bf16 GEMM",
+        "bound": "tensor", "peak": peaks["bf16"], "unit": "TFLOP/s", **tensor(bwd_tf),
+        "peak_source": f"{peaks['source']} burst bf16 GEMM; frac_of_sustained uses the sustained one",
+        "timing": "CUDA events between the calls of the timed steps themselves: fwd + pre + bwd = ms_per_step",
         "traffic": traffic_bytes(d, mode, lb * lh, n),
-        "traffic_note": "dram__bytes_read+write per launch(es) of the backward-main kernel(s) from the "
-                        "ncu capture in profiles/attention_kernels_c3small_ncu.md (24 batch*head "
-                        "problems, d=128, N=8192), scaled by batch*head; null for other shapes",
+        "traffic_note": "dram__bytes_read+write of the backward-main kernel(s) per step, from an ncu capture of "
+                        "24 batch*head problems (d=128, N=8192) scaled by batch*head; null for other shapes",
         "algorithmic_flops": 2.5 * my_fwd_flops,
-        "fwd": {"achieved": fwd_tf, "frac": fwd_tf / peaks["bf16"], "ms": ms_fwd},
+        "fwd": {**tensor(fwd_tf), "ms": ms_fwd},
         "bwd_ms": ms_bwd,
-        "preprocess": {"bound": "hbm", "achieved": pre_bytes / (ms_pre * 1e-3) / 1e9,
-                       "peak": peaks["hbm"], "unit": "GB/s",
-                       "frac": pre_bytes / (ms_pre * 1e-3) / 1e9 / peaks["hbm"], "ms": ms_pre},
+        "preprocess": hbm(pre_bytes, ms_pre),
+        "sum_of_parts_ms": ms_fwd + ms_pre + ms_bwd,
     }
+    if "bwd_first" in parts and d <= 128:
+        # dK/dV kernel: 4 of the 5 tile products of the backward; second kernel: the fifth (spill:
+        # bound by reading the 32 KiB dS tile and the K tile per product) or, recomputing, 3 more
+        t1, t2 = parts["bwd_first"], parts["bwd_second"]
+        tiles = (n + 127) // 128
+        roofline["bwd_dkdv_kernel"] = {**tensor(0.8 * 2.5 * my_fwd_flops / (t1 * 1e-3) / 1e12), "ms": t1,
+                                       "algorithmic_flops": 0.8 * 2.5 * my_fwd_flops}
+        if mode == 2:
+            scratch = lb * lh * tiles * (tiles + 1) // 2 * 32768
+            roofline["bwd_consume_kernel"] = {
+                **hbm(scratch + 2.0 * lb * lh * n * d * 2, t2),
+                "bytes": "the dS scratch read once + K read and dQ written once (K tiles are re-read from L2)",
+                "tensor_frac": 0.2 * 2.5 * my_fwd_flops / (t2 * 1e-3) / 1e12 / peaks["bf16"]}
+        else:
+            roofline["bwd_dq_kernel"] = {**tensor(0.2 * 2.5 * my_fwd_flops / (t2 * 1e-3) / 1e12), "ms": t2,
+                                         "note": "3 tile products and the exponentials run for 1 counted"}
 
     # ------------------------------------------------------------ end to end (host buffers)
     e2e = None
@@ -435,6 +519,7 @@ def main():
             e2e_step()
         torch.cuda.synchronize()
         e_steps = max(3, min(args.steps, 10))
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         ev0.record()
         for _ in range(e_steps):
@@ -456,18 +541,42 @@ def main():
     sustained = None
     if args.sustain_seconds > 0:
         n_sus = max(args.steps, int(args.sustain_seconds * 1e3 / ms_per_step))
-        barrier()
         with ClockSampler(local_rank) as sus_clocks:
-            ev0.record()
-            for _ in range(n_sus):
-                step()
-            ev1.record()
-            torch.cuda.synchronize()
-        barrier()
-        sus_ms = max_over_ranks(ev0.elapsed_time(ev1)) / n_sus
-        sustained = {"steps": n_sus, "ms_per_step": sus_ms,
-                     "value": 3.5 * total_fwd_flops / (sus_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                     "clocks": sus_clocks.summary()}
+            sus_ms, _ = prob.timed(n_sus, 0)
+        sus_value = 3.5 * total_fwd_flops / (sus_ms * 1e-3) / 1e12
+        sus_clock = sus_clocks.summary()
+        sustained = {"steps": n_sus, "ms_per_step": sus_ms, "value": sus_value, "unit": "TFLOP/s",
+                     "frac_of_sustained_peak": sus_value / world / peaks["bf16_sustained"],
+                     "clocks": sus_clock,
+                     # time x clock: what the step costs in SM cycles, comparable between GPUs of the
+                     # pool and between runs whose power state differs
+                     "mcycles_per_step": sus_ms * sus_clock["sm_mhz"] / 1e3 if sus_clock["sm_mhz"] else None}
+
+    # ------------------------------------------------------------ strong scaling of the two split
+    # configurations: one seeded global problem, each rank its contiguous (batch, head) slab
+    # (shard_slab), no collective on the data path; value = whole-job FLOPs / slowest rank's time.
+    def strong_leg(name, steps, warmup):
+        lb_, lh_, n_, d_, dtype_, qk_, sc_ = WORKLOADS[name]
+        if lb_ * lh_ % world:
+            return {"skipped": f"{lb_ * lh_} problems do not split evenly over {world} GPUs"}
+        tensors = tuple(shard_slab(t, world, rank).contiguous()
+                        for t in make_inputs((lb_, lh_, n_, d_), dtype_, 0, qk_))
+        p_ = Problem(tensors, n_, d_, 0 if dtype_ == torch.float16 else 1, sc_ or 1.0 / math.sqrt(d_),
+                     api._backward_mode(bool(det), d_, n_))
+        ms_, _ = p_.timed(steps, warmup)
+        flops = 3.5 * fwd_flops(lb_, lh_, n_, d_)
+        return {"workload": name, "shape": [lb_, lh_, n_, d_], "batch_heads_per_gpu": lb_ * lh_ // world,
+                "steps": steps, "ms_per_step": ms_, "value": flops / (ms_ * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "per_gpu_tflops": flops / (ms_ * 1e-3) / 1e12 / world,
+                "frac_of_burst_peak": flops / (ms_ * 1e-3) / 1e12 / world / peaks["bf16"]}
+
+    strong = None
+    if args.workload == "c3" and args.scaling == "weak" and not args.no_strong:
+        del prob.ws  # the legs bring their own scratch
+        torch.cuda.empty_cache()
+        strong = {"c4": strong_leg("c4", max(3, args.steps // 4), 3)}
+        if world > 1:
+            strong["c3"] = strong_leg("c3", args.steps, args.warmup)
 
     st = _lib.device_status()
     if st != 0:
@@ -485,12 +594,15 @@ def main():
                              "nominal_2250": value / world / 2250.0, "source": peaks["source"]},
             "clocks": clocks.summary(),
             "sustained": sustained,
+            "strong": strong,
             "gpu_launches": launches_per_step * args.steps,
             "roofline": roofline,
             "e2e": e2e,
         }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(b, h, n, d, dtype, qk_mul, scale_opt)
+        if world == 1 and not args.no_triton_reference and args.workload in ("c2", "c3"):
+            line["triton_reference"] = triton_reference(args.workload, ms_per_step)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

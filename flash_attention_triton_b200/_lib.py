@@ -25,6 +25,7 @@ SYMBOLS = [
     ("fa2_bwd", c_int, [c_void_p] * 9 + [c_size_t] + [c_int] * 5 + [c_float, c_int, c_void_p]),
     ("fa2_bwd_workspace_bytes", c_size_t, [c_int] * 5),
     ("fa2_set_spill_budget", c_size_t, [c_size_t]),
+    ("fa2_bwd_mark_between", c_int, [c_void_p]),
     ("fa2_device_status", c_int, [ctypes.POINTER(c_int)]),
     ("fa2_selftest_mma", c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     ("fa2_selftest_wait_timeout", c_int, [c_void_p]),

@@ -27,6 +27,16 @@ namespace {
 
 constexpr int kMaxDevices = 64;
 
+// fa2_bwd_mark_between: event the next two-kernel backward of this thread records between its
+// kernels (one-shot).
+thread_local cudaEvent_t t_mark_between = nullptr;
+void record_mark_between(cudaStream_t st) {
+  if (t_mark_between) {
+    cudaEventRecord(t_mark_between, st);
+    t_mark_between = nullptr;
+  }
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                    const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -378,6 +388,7 @@ static int bwd_strided(const void* q, const void* k, const void* v, const void* 
     cudaError_t ce =
         launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rs, nullptr, 0, d->status, st);
     if (ce != cudaSuccess) return static_cast<int>(ce);
+    record_mark_between(st);
     return static_cast<int>(launch_bwd_dq(s, tq, tk, tv, tdo, tdq, rs, d->status, st));
   }
   if (deterministic == 2) {
@@ -399,6 +410,7 @@ static int bwd_strided(const void* q, const void* k, const void* v, const void* 
     cudaError_t ce =
         launch_bwd_dkdv(s, tq, tk, tv, tdo, tdk, tdv, rs, scratch, 2, d->status, st);
     if (ce != cudaSuccess) return static_cast<int>(ce);
+    record_mark_between(st);
     return static_cast<int>(launch_bwd_consume(s, 2, scratch, tk, tdq, rs, d->status, st));
   }
   float* dq_accum = static_cast<float*>(workspace);
@@ -428,6 +440,11 @@ int fa2_bwd(const void* q, const void* k, const void* v, const void* dout, const
             int N, int D, int dtype, float scale, int deterministic, fa2_stream_t stream) {
   return fa2_bwd_strided(q, k, v, dout, rowstats, dq, dk, dv, workspace, workspace_bytes, B, H, N,
                          N, D, dtype, scale, deterministic, nullptr, stream);
+}
+
+int fa2_bwd_mark_between(void* event) {
+  t_mark_between = static_cast<cudaEvent_t>(event);
+  return FA2_OK;
 }
 
 size_t fa2_set_spill_budget(size_t bytes) {

@@ -176,6 +176,15 @@ int fa2_bwd_strided(const void* q, const void* k, const void* v, const void* dou
                     int deterministic, const long long* strides, fa2_stream_t stream);
 
 /*
+ * Diagnostics for benchmarks: the next fa2_bwd call of the calling thread that runs two kernels
+ * (deterministic == 1: dK/dV kernel, dQ kernel; deterministic == 2 at D <= 128: dK/dV kernel,
+ * dQ consumer kernel; the first chunk when the call is chunked) records `event`, a cudaEvent_t, on
+ * its stream between the two, so that the two parts of one call can be timed in place.  One
+ * shot: the event is forgotten once recorded; NULL cancels.  No counterpart in the reference.
+ */
+int fa2_bwd_mark_between(void* event);
+
+/*
  * Reads and clears the per-device status word that kernels set when a bounded wait
  * expires (they then drain and return instead of hanging).  Synchronises the device.
  * *status_out = 0 when every kernel since the last call ran to completion.
