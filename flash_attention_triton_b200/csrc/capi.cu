@@ -271,15 +271,15 @@ int fa2_bwd_preprocess_strided(const void* o, const void* dout, const float* lse
   if (!o || !dout || !lse || !rowstats) return FA2_ERR_NULL_POINTER;
   if (int e = check_shape(B, H, N, D, dtype)) return e;
   if (!aligned16(o) || !aligned16(dout) || !aligned16(rowstats)) return FA2_ERR_MISALIGNED;
-  if (static_cast<long long>(B) * H * ((N + 127) / 128) > 0x7fffffffll) return FA2_ERR_SHAPE;  // one block per tile
+  if (static_cast<long long>(B) * H * ((N + 127) / 128) > 0x7fffffffll) return FA2_ERR_SHAPE;  // one block per tile (head dim 256)
   Strides so, sdo;
   if (int e = get_strides(strides, 0, B, H, N, D, &so)) return e;
   if (int e = get_strides(strides, 1, B, H, N, D, &sdo)) return e;
   DeviceState* d = nullptr;
   if (int e = device_state(&d)) return e;
   const AttnShape s = make_shape(B, H, N, N, D, dtype, 1.f);
-  return static_cast<int>(launch_bwd_preprocess(s, o, so, dout, sdo, lse, rowstats,
-                                                static_cast<cudaStream_t>(stream)));
+  return static_cast<int>(launch_bwd_preprocess(s, o, so, dout, sdo, lse, rowstats, d->status,
+                                                d->num_sms, static_cast<cudaStream_t>(stream)));
 }
 
 int fa2_bwd_preprocess(const void* o, const void* dout, const float* lse, float* rowstats, int B,

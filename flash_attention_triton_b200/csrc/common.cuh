@@ -132,7 +132,8 @@ cudaError_t launch_fwd(const AttnShape& s, const CUtensorMap& tq, const CUtensor
 // 16-bit pattern with the sign cleared.
 cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strides& so,
                                   const void* dout, const Strides& sdo, const float* lse,
-                                  float* rowstats, cudaStream_t stream);
+                                  float* rowstats, int* status, int num_sms,
+                                  cudaStream_t stream);
 
 // dK/dV per KV tile.  mode 1 also accumulates dQ into dq_accum with fp32 atomic adds
 // (dq_accum layout: [bh][t][w = 4][k = D/4][lane = 32][4] floats, holding element

@@ -124,6 +124,204 @@ __global__ void __launch_bounds__(kPreThreads)
   }
 }
 
+// ----------------------------------------------------------------------------------------
+// The same computation as a persistent kernel fed by the copy engine (head dims up to 128).
+//
+// One CTA per SM walks the 128-row tiles blockIdx.x, blockIdx.x + gridDim.x, ...  A producer warp
+// keeps a ring of shared-memory stages full with untiled bulk copies (one stage = the o rows and
+// the dout rows of one tile; one copy per tensor when its rows are contiguous in memory, else one
+// copy per row), so the bytes in flight per SM stay near the ring size (128 - 192 KiB) whatever
+// the eight consumer warps are doing; the block-per-tile kernel above has nothing in flight while
+// a block reduces and stores, and reaches less than half of the HBM rate.  Consumers read their
+// pieces from shared memory with the row / lane assignment of the kernel above, free the stage as
+// soon as the pieces are in registers, and hand the tile's 256 results to the next iteration,
+// which stores them with one coalesced 1 KiB write.  lse of the next tile is fetched one
+// iteration ahead.  Rows in shared memory are packed at their true width (d8 pieces).
+// ----------------------------------------------------------------------------------------
+template <int D>
+struct PreRing {
+  static constexpr int kTileBytes = 128 * D * 2;      // one tensor's rows at the padded width
+  static constexpr int kStageBytes = 2 * kTileBytes;  // o, then dout
+  static constexpr int kStages = D == 128 ? 3 : (D == 64 ? 6 : 8);
+  static constexpr int kConsumers = 256;
+  static constexpr int kThreads = kConsumers + 32;
+  // after the stages: full / empty barriers, two result buffers of 256 floats, two of 8 maxima
+  static constexpr int kOffBars = kStages * kStageBytes;
+  static constexpr int kOffStat = kOffBars + 16 * kStages;
+  static constexpr int kOffMax = kOffStat + 2 * 256 * 4;
+  static constexpr int kOffAbort = kOffMax + 2 * 8 * 4;
+  static constexpr int kSmemBytes = kOffAbort + 16;
+};
+
+enum PreSite { kPSiteProducer = 64, kPSiteConsumer };
+
+// All consumer threads learn whether every one of them got its stage (they leave together).
+__device__ __forceinline__ bool consumers_all(bool ok, int nthreads) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "barrier.cta.red.and.pred p, 1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r)
+      : "r"(static_cast<uint32_t>(ok)), "r"(nthreads)
+      : "memory");
+  return r != 0;
+}
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(PreRing<D>::kThreads, 1)
+    bwd_preprocess_ring_kernel(const uint4* __restrict__ o, const uint4* __restrict__ dout,
+                               const float* __restrict__ lse, float* __restrict__ rowstats,
+                               unsigned* __restrict__ tile_amax, int N, int ntiles,
+                               long long tiles, int d8, int H, Strides so, Strides sdo,
+                               int* status) {
+  using R = PreRing<D>;
+  constexpr int kLanesPerRow = D / 8;
+  constexpr int kRowsPerPass = R::kConsumers / kLanesPerRow;  // 64, 32 or 16
+  constexpr int kPasses = 128 / kRowsPerPass;                 // 2, 4 or 8
+  extern __shared__ __align__(128) unsigned char smem[];
+  const uint32_t base = smem_u32(smem);
+  auto full = [&](int s) { return base + R::kOffBars + 16u * s; };
+  auto empty = [&](int s) { return base + R::kOffBars + 16u * s + 8u; };
+  float* stat = reinterpret_cast<float*>(smem + R::kOffStat);
+  unsigned* wmax = reinterpret_cast<unsigned*>(smem + R::kOffMax);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + R::kOffAbort);
+  const WaitCtx w{abort_flag, status};
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < R::kStages; ++s) {
+      mbar_init(full(s), 1);
+      mbar_init(empty(s), R::kConsumers / 32);
+    }
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const uint32_t row_bytes = static_cast<uint32_t>(d8) * 16u;
+
+  if (warp == R::kConsumers / 32) {
+    // ---------------- producer warp ----------------
+    int it = 0;
+    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+      const int s = it % R::kStages;
+      const uint32_t ph = (it / R::kStages) & 1;
+      if (!mbar_wait_warp(empty(s), ph ^ 1, w, kPSiteProducer)) break;
+      const long long bh = tile / ntiles;
+      const int t = static_cast<int>(tile - bh * ntiles);
+      const long long bb = bh / H, hh = bh - bb * H;
+      const int rows = min(128, N - t * 128);
+      if (lane == 0) mbar_arrive_expect_tx(full(s), 2u * rows * row_bytes);
+      __syncwarp();
+      const uint32_t dst = base + s * R::kStageBytes;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const Strides& st = which ? sdo : so;
+        const uint4* src = (which ? dout : o) + bb * st.b + hh * st.h +
+                           static_cast<long long>(t) * 128 * st.n;
+        const uint32_t d0 = dst + which * R::kTileBytes;
+        if (st.n == d8) {
+          if (lane == 0) bulk_load_1d(d0, src, rows * row_bytes, full(s));
+        } else {
+          for (int r = lane; r < rows; r += 32)
+            bulk_load_1d(d0 + r * row_bytes, src + static_cast<long long>(r) * st.n, row_bytes,
+                         full(s));
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumer warps ----------------
+  const int sub = threadIdx.x % kLanesPerRow;
+  const int row_in_pass = threadIdx.x / kLanesPerRow;
+  float lse_cur[kPasses], lse_nxt[kPasses];
+  auto fetch_lse = [&](long long tile, float* dst) {
+    const long long bh = tile / ntiles;
+    const int t = static_cast<int>(tile - bh * ntiles);
+#pragma unroll
+    for (int i = 0; i < kPasses; ++i) {
+      const int row = t * 128 + i * kRowsPerPass + row_in_pass;
+      dst[i] = (sub == 0 && tile < tiles && row < N) ? __ldg(lse + bh * N + row) : INFINITY;
+    }
+  };
+  fetch_lse(blockIdx.x, lse_cur);
+  int it = 0;
+  long long prev_tile = -1;
+  for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
+    const int s = it % R::kStages;
+    const uint32_t ph = (it / R::kStages) & 1;
+    fetch_lse(tile + gridDim.x, lse_nxt);
+    const bool ok = mbar_wait(full(s), ph, w, kPSiteConsumer);
+    if (!consumers_all(ok, R::kConsumers)) return;
+    // the previous tile's results are complete in shared memory: one coalesced store
+    if (prev_tile >= 0) {
+      const int pb = (it - 1) & 1;
+      rowstats[prev_tile * 256 + threadIdx.x] = stat[pb * 256 + threadIdx.x];
+      if (threadIdx.x == 0) {
+        unsigned m = wmax[pb * 8];
+#pragma unroll
+        for (int i = 1; i < 8; ++i) m = max(m, wmax[pb * 8 + i]);
+        tile_amax[prev_tile] = m;
+      }
+    }
+    const int t = static_cast<int>(tile % ntiles);
+    const int rows = min(128, N - t * 128);
+    const uint4* so_ = reinterpret_cast<const uint4*>(smem + s * R::kStageBytes);
+    const uint4* sdo_ = reinterpret_cast<const uint4*>(smem + s * R::kStageBytes + R::kTileBytes);
+    uint4 a[kPasses], b[kPasses];
+#pragma unroll
+    for (int i = 0; i < kPasses; ++i) {
+      const int r = i * kRowsPerPass + row_in_pass;
+      if (r < rows && sub < d8) {
+        a[i] = so_[r * d8 + sub];
+        b[i] = sdo_[r * d8 + sub];
+      } else {
+        a[i] = make_uint4(0, 0, 0, 0);
+        b[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty(s));  // the pieces are in registers
+    unsigned amax2 = 0;
+    const int cb = it & 1;
+#pragma unroll
+    for (int i = 0; i < kPasses; ++i) {
+      float acc = dot8<BF16>(a[i], b[i]);
+#pragma unroll
+      for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
+        acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      amax2 = __vmaxu2(amax2, b[i].x & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].y & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].z & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].w & 0x7fff7fffu);
+      const int r = i * kRowsPerPass + row_in_pass;
+      if (sub == 0) {
+        const bool valid = r < rows;
+        stat[cb * 256 + r] = valid ? -lse_cur[i] * kLog2e : -INFINITY;
+        stat[cb * 256 + 128 + r] = valid ? -acc : 0.f;
+      }
+    }
+    unsigned m = max(amax2 & 0xffffu, amax2 >> 16);
+    m = __reduce_max_sync(0xffffffffu, m);
+    if (lane == 0) wmax[cb * 8 + warp] = m;
+#pragma unroll
+    for (int i = 0; i < kPasses; ++i) lse_cur[i] = lse_nxt[i];
+    prev_tile = tile;
+  }
+  if (prev_tile >= 0) {
+    named_bar_sync(1, R::kConsumers);
+    const int pb = (it - 1) & 1;
+    rowstats[prev_tile * 256 + threadIdx.x] = stat[pb * 256 + threadIdx.x];
+    if (threadIdx.x == 0) {
+      unsigned m = wmax[pb * 8];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) m = max(m, wmax[pb * 8 + i]);
+      tile_amax[prev_tile] = m;
+    }
+  }
+}
+
 // One thread converts 8 consecutive head-dim elements of one row.  Consecutive lanes take
 // consecutive rows of the same 32-row group, so the fp32 reads are contiguous 512-byte runs
 // (the layout the fused backward kernel accumulates into).
@@ -161,14 +359,26 @@ Strides in_vec8(const Strides& st) { return Strides{st.b / 8, st.h / 8, st.n / 8
 
 template <int D, bool BF16>
 cudaError_t launch_pre_t(const AttnShape& s, const void* o, const Strides& so, const void* dout,
-                         const Strides& sdo, const float* lse, float* rowstats,
-                         cudaStream_t stream) {
+                         const Strides& sdo, const float* lse, float* rowstats, int* status,
+                         int num_sms, cudaStream_t stream) {
   const int ntiles = (s.N + 127) / 128;
   const long long tiles = static_cast<long long>(s.B) * s.H * ntiles;
   unsigned* tile_amax = reinterpret_cast<unsigned*>(rowstats + tiles * 256);  // behind the last tile
-  bwd_preprocess_kernel<D, BF16><<<static_cast<unsigned>(tiles), kPreThreads, 0, stream>>>(
-      static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, tile_amax, s.N,
-      ntiles, s.Dg / 8, s.H, in_vec8(so), in_vec8(sdo));
+  if constexpr (D <= 128) {
+    using R = PreRing<D>;
+    auto* kernel = bwd_preprocess_ring_kernel<D, BF16>;
+    const cudaError_t attr = cudaFuncSetAttribute(
+        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R::kSmemBytes);
+    if (attr != cudaSuccess) return attr;
+    const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
+    kernel<<<grid, R::kThreads, R::kSmemBytes, stream>>>(
+        static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, tile_amax,
+        s.N, ntiles, tiles, s.Dg / 8, s.H, in_vec8(so), in_vec8(sdo), status);
+  } else {
+    bwd_preprocess_kernel<D, BF16><<<static_cast<unsigned>(tiles), kPreThreads, 0, stream>>>(
+        static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, tile_amax,
+        s.N, ntiles, s.Dg / 8, s.H, in_vec8(so), in_vec8(sdo));
+  }
   return cudaGetLastError();
 }
 
@@ -188,11 +398,15 @@ cudaError_t launch_cvt_t(const AttnShape& s, const float* dq_accum, void* dq, co
 
 cudaError_t launch_bwd_preprocess(const AttnShape& s, const void* o, const Strides& so,
                                   const void* dout, const Strides& sdo, const float* lse,
-                                  float* rowstats, cudaStream_t stream) {
-#define FA2_CASE(DD)                                                                 \
-  case DD:                                                                           \
-    return s.dtype ? launch_pre_t<DD, true>(s, o, so, dout, sdo, lse, rowstats, stream)  \
-                   : launch_pre_t<DD, false>(s, o, so, dout, sdo, lse, rowstats, stream);
+                                  float* rowstats, int* status, int num_sms,
+                                  cudaStream_t stream) {
+#define FA2_CASE(DD)                                                                          \
+  case DD:                                                                                    \
+    return s.dtype                                                                            \
+               ? launch_pre_t<DD, true>(s, o, so, dout, sdo, lse, rowstats, status, num_sms,  \
+                                        stream)                                               \
+               : launch_pre_t<DD, false>(s, o, so, dout, sdo, lse, rowstats, status, num_sms, \
+                                         stream);
   switch (s.D) {
     FA2_CASE(32)
     FA2_CASE(64)
