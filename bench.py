@@ -16,14 +16,29 @@ Printed JSON (one line, rank 0):
                tensors: host->device copies of q,k,v,dO and device->host copies of o,dq,dk,dv are
                inside the timed region, every step; copy-in, compute and copy-out of
                neighbouring steps overlap on three streams.
-  roofline     tensor-core roofline of the dominant kernel (backward main), achieved = its
-               algorithmic FLOPs / its own average launch duration (CUDA events around that
-               launch), peak = MEASURED_PEAKS.json bf16_tflops (burst; kernel timed alone).
+  roofline     the backward-main call against the tensor roofline (achieved = its algorithmic
+               FLOPs / its average duration, peak = MEASURED_PEAKS.json bf16_tflops), and one entry
+               per kernel of the step: fwd, preprocess (HBM), bwd_dkdv_kernel, and
+               bwd_consume_kernel (HBM: it reads the spilled dS tiles) or bwd_dq_kernel.  Every
+               duration comes from CUDA events recorded between the calls of the timed steps
+               themselves (the one between the two backward kernels through fa2_bwd_mark_between),
+               so sum_of_parts_ms = ms_per_step up to the event overhead.  traffic = DRAM bytes of
+               the backward-main kernels per step from an ncu capture (see NCU_BWD_DRAM_MB_PER_24).
+               At head dims 32 and 64 the entries carry softmax_ceiling (see softmax_ceiling).
   sustained    the same device-resident step run back to back for about a second under the
                clock sampler (the timed region is too short for NVML's clock averaging):
-               steps, ms_per_step, value and the clocks / throttle reasons seen.
+               steps, ms_per_step, value, its fraction of the sustained GEMM peak, the clocks /
+               throttle reasons seen, and mcycles_per_step = ms x median SM MHz (comparable
+               between GPUs and power states).
+  strong       strong-scaling legs (default workload only): the c4 shape [1,16,32768,128] and, at
+               N > 1, the c3 shape, split over the ranks by (batch, head) with shard_slab;
+               value = whole-job FLOPs / slowest rank's time.  --no-strong leaves them out.
+  triton_reference  the reference's own Triton kernels timed on this GPU in a child process, when
+               the reference is installed under baseline/_ref (N=1 only; --no-triton-reference).
   cpu_baseline naive fp32 PyTorch causal attention fwd+bwd on the host cores over a bounded
                sample of the same workload's heads (rank 0, N=1 only).
+  clocks, gpu_launches  SM clock / throttle reasons sampled during the timed region; kernels of
+               this library launched inside it.
 
 Multi-GPU: one process per GPU (torchrun); every (batch, head) problem is independent, so
 ranks share nothing on the data path.  --scaling weak (default): every rank runs the whole
@@ -65,11 +80,36 @@ METRIC = "causal attn fwd+bwd TFLOP/s, bf16 N=8192 d=128"
 
 
 # DRAM bytes (read + write) of the backward-main kernels measured by ncu on the reduced C3
-# workload (24 batch*head problems, N=8192, d=128): fused kernel 303.7 + 159.2 MB; the
-# recompute pair 203.2 + 76.1 MB (dK/dV) plus 202.9 + 37.9 MB (dQ); the spill pair
-# 208.2 + 1679.1 MB (dK/dV, writes the dS tiles) plus 1686.1 + 51.8 MB (dQ, reads them back).
-NCU_BWD_DRAM_MB_PER_24 = {0: 303.7 + 159.2, 1: 203.2 + 76.1 + 202.9 + 37.9,
-                          2: 208.2 + 1679.1 + 1686.1 + 51.8}
+# workload (24 batch*head problems, N=8192, d=128): fused kernel 381.8 + 209.7 MB and the convert
+# 100.7 + 20.1 MB; the recompute pair 203.2 + 76.1 MB (dK/dV) plus 204.3 + 36.8 MB (dQ); the spill
+# pair 329.6 + 1679.5 MB (dK/dV, writes the dS tiles) plus 1744.1 + 46.2 MB (dQ, reads them back).
+NCU_BWD_DRAM_MB_PER_24 = {0: 381.8 + 209.7 + 100.7 + 20.1, 1: 203.2 + 76.1 + 204.3 + 36.8,
+                          2: 329.6 + 1679.5 + 1744.1 + 46.2}
+
+# Polynomial share of the exponentials (of every 8 column pairs) the kernels are built with
+# (FA2_FWD_POLY_PAIRS_PER_8 in csrc/fwd.cu, FA2_BWD_POLY_PAIRS_PER_8 in csrc/bwd_roles.cuh).
+POLY_SHARE = {"fwd": 3 / 8, "bwd": 4 / 8}
+
+
+def softmax_ceiling(d, which):
+    """Upper bound on the tensor-pipe fraction of a 128 x 128 score tile set by the softmax work.
+
+    Per SM and tile: the tensor pipe needs 8 d cycles in the forward (2 tile products) and 20 d in
+    the dK/dV kernel (5 products counted at 8192 dense 16-bit FLOP / clk / SM); the 16384
+    exponentials need 1024 (1 - p) cycles of the MUFU (16 / clk / SM) for a polynomial share p;
+    all the per-element instructions (scale, max, sum, pack; in the backward also dP - delta and
+    the product with P) plus the MUFU issues and about 5.5 instructions per polynomial
+    exponential share 128 issue slots / clk / SM.  The slower of the two is the floor under the
+    tile time; at d = 128 it is below the tensor time, at d <= 64 above it.
+    """
+    p = POLY_SHARE[which]
+    base = 2.5 if which == "fwd" else 6.0
+    mufu = 1024.0 * (1.0 - p)
+    issue = 16384.0 * (base + (1.0 - p) + 5.5 * p) / 128.0
+    tensor_cycles = (8.0 if which == "fwd" else 20.0) * d
+    floor = max(mufu, issue)
+    return {"tensor_cycles": tensor_cycles, "mufu_cycles": mufu, "issue_cycles": issue,
+            "frac_of_tensor_peak": min(1.0, tensor_cycles / floor)}
 
 
 def traffic_bytes(d, mode, batch_heads, n=8192):
@@ -444,6 +484,14 @@ def main():
     tensor = lambda tf: {"achieved": tf, "frac": tf / peaks["bf16"], "frac_of_sustained": tf / peaks["bf16_sustained"]}
     hbm = lambda nbytes, ms: {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peaks["hbm"],
                               "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm"], "ms": ms}
+    def ceiling(which, tf):
+        # head dims 32 and 64: the softmax work, not the tensor pipe, bounds a tile
+        c = softmax_ceiling(d, which)
+        if c["frac_of_tensor_peak"] >= 1.0:
+            return {}
+        top = c["frac_of_tensor_peak"] * peaks["bf16"]
+        return {"bound": "exp", "softmax_ceiling": {**c, "tflops": top, "frac": tf / top}}
+
     roofline = {
         "kernel": "bwd_scores_wide_kernel + bwd_consume_kernel x3 (dV, dK, dQ)" if d > 128 else (
             "bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert",
@@ -456,7 +504,7 @@ def main():
         "traffic_note": "dram__bytes_read+write of the backward-main kernel(s) per step, from an ncu capture of "
                         "24 batch*head problems (d=128, N=8192) scaled by batch*head; null for other shapes",
         "algorithmic_flops": 2.5 * my_fwd_flops,
-        "fwd": {**tensor(fwd_tf), "ms": ms_fwd},
+        "fwd": {**tensor(fwd_tf), "ms": ms_fwd, **ceiling("fwd", fwd_tf)},
         "bwd_ms": ms_bwd,
         "preprocess": hbm(pre_bytes, ms_pre),
         "sum_of_parts_ms": ms_fwd + ms_pre + ms_bwd,
@@ -466,8 +514,9 @@ def main():
         # bound by reading the 32 KiB dS tile and the K tile per product) or, recomputing, 3 more
         t1, t2 = parts["bwd_first"], parts["bwd_second"]
         tiles = (n + 127) // 128
-        roofline["bwd_dkdv_kernel"] = {**tensor(0.8 * 2.5 * my_fwd_flops / (t1 * 1e-3) / 1e12), "ms": t1,
-                                       "algorithmic_flops": 0.8 * 2.5 * my_fwd_flops}
+        dkdv_tf = 0.8 * 2.5 * my_fwd_flops / (t1 * 1e-3) / 1e12
+        roofline["bwd_dkdv_kernel"] = {**tensor(dkdv_tf), "ms": t1, "algorithmic_flops": 0.8 * 2.5 * my_fwd_flops,
+                                       **ceiling("bwd", dkdv_tf)}
         if mode == 2:
             scratch = lb * lh * tiles * (tiles + 1) // 2 * 32768
             roofline["bwd_consume_kernel"] = {

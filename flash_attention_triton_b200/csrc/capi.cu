@@ -175,6 +175,12 @@ long long spill_bytes_per_head(int N, int Nk, int D) {
 // What fa2_bwd_workspace_bytes recommends at most (fa2_set_spill_budget); a workspace of any size
 // that holds one head is accepted by fa2_bwd.
 std::atomic<long long> g_spill_budget{8ll << 30};
+// Tiles (= CTAs of the dK/dV and of the dQ kernel) a chunk should have.  Smaller chunks leave SMs
+// idle at the end of every launch: at N = 8192, d = 128 on 148 SMs, chunks of 2048 tiles cost
+// 0.5 % against a single chunk of 4096, 1024 tiles 3 %, 512 tiles 11 %, 256 tiles 21 %, 64 tiles
+// (one head) 290 %.  More scratch than this buys nothing, so the recommendation grows with N
+// (about 256 KiB per row of a head), not with B * H * N^2.
+constexpr long long kSpillChunkTiles = 2048;
 
 // Spill mode (and head dims above 128, which have no other backward): the problem is worked
 // through in chunks of whole batch entries, or of head ranges of one batch entry, that fit the
@@ -291,10 +297,14 @@ size_t fa2_bwd_workspace_bytes(int B, int H, int N, int D, int deterministic) {
   if (B <= 0 || H <= 0 || N <= 0 || D <= 0) return 0;
   const long long BH = static_cast<long long>(B) * H;
   if (deterministic == 2 || D > 128) {
-    // 16-bit [128 x 128] tiles of whole heads: all of them when the budget allows (one chunk is
-    // fastest), else what the chunk plan uses of the budget, never less than one head
+    // 16-bit [128 x 128] tiles of whole heads: as many heads as make a chunk of
+    // kSpillChunkTiles tiles, within the budget, never less than one head; then what the chunk
+    // plan uses of that
     const long long per_head = spill_bytes_per_head(N, N, D);
-    const SpillPlan plan = spill_plan(B, H, per_head, std::max(per_head, g_spill_budget.load()));
+    const long long ntiles = (static_cast<long long>(N) + 127) / 128;
+    const long long want = (kSpillChunkTiles + ntiles - 1) / ntiles * per_head;
+    const SpillPlan plan =
+        spill_plan(B, H, per_head, std::max(per_head, std::min(want, g_spill_budget.load())));
     return static_cast<size_t>(plan.nb) * plan.nh * static_cast<size_t>(per_head);
   }
   if (deterministic == 1) return 0;

@@ -148,14 +148,19 @@ def test_key_count_must_not_exceed_query_count():
 
 
 def test_spill_scratch_size_follows_the_budget():
-    """32 KiB per (KV tile, Q tile) pair, bounded by fa2_set_spill_budget through chunking."""
+    """32 KiB per (KV tile, Q tile) pair; chunks of whole heads of about 2048 tiles, so the
+    recommendation is linear in N and independent of B*H; bounded by fa2_set_spill_budget."""
     lib = _lib.lib()
     pairs = 64 * 65 // 2  # N = 8192: 64 tiles
     previous = lib.fa2_set_spill_budget(1 << 40)
     try:
-        assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == 2 * 32 * pairs * 32768
-        lib.fa2_set_spill_budget(40 * pairs * 32768)      # one batch entry (32 heads) fits, two do not
+        # 2048 tiles = 32 heads of 64 tiles, whatever the number of heads beyond that
         assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == 32 * pairs * 32768
+        assert lib.fa2_bwd_workspace_bytes(8, 32, 8192, 128, 2) == 32 * pairs * 32768
+        assert lib.fa2_bwd_workspace_bytes(1, 8, 8192, 128, 2) == 8 * pairs * 32768  # all there is
+        # four times the rows: a quarter of the heads, 4x the bytes (not 16x)
+        pairs4 = 256 * 257 // 2
+        assert lib.fa2_bwd_workspace_bytes(2, 32, 32768, 128, 2) == 8 * pairs4 * 32768
         lib.fa2_set_spill_budget(20 * pairs * 32768)      # 20 heads fit: two chunks of 16
         assert lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2) == 16 * pairs * 32768
         assert lib.fa2_bwd_workspace_bytes(2, 16, 8192, 256, 0) == 8 * 2 * pairs * 32768  # 64 KiB per pair: 10 heads fit, two chunks of 8
@@ -192,7 +197,7 @@ def test_workspace_allocation_falls_back_when_memory_is_short(monkeypatch):
     lib = _lib.lib()
     head = 2080 * 32768
     want = lib.fa2_bwd_workspace_bytes(2, 32, 8192, 128, 2)
-    assert want == 64 * head
+    assert want == 32 * head  # chunks of 2048 tiles
     calls, limit = [], [1 << 62]
 
     def fake_empty(nbytes, device=None, dtype=None):
@@ -203,13 +208,13 @@ def test_workspace_allocation_falls_back_when_memory_is_short(monkeypatch):
 
     monkeypatch.setattr(api.torch, "empty", fake_empty)
     assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_SPILL)[1:] == (want, api._MODE_SPILL)
-    limit[0] = 1 << 30  # 8 heads fit
+    limit[0] = 1 << 29  # 7 heads fit
     calls.clear()
-    assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_SPILL)[1:] == (8 * head, api._MODE_SPILL)
+    assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_SPILL)[1:] == (4 * head, api._MODE_SPILL)
     limit[0] = 100 << 20  # one head (68 MB) fits
     calls.clear()
     assert api._allocate_workspace(lib, "cpu", 2, 32, 8192, 128, api._MODE_SPILL)[1:] == (head, api._MODE_SPILL)
-    assert calls == [want, 8 * head, head]
+    assert calls == [want, 4 * head, head]
     # exactly what fa2_bwd accepts as the minimum: refused with one byte less
     assert lib.fa2_bwd(*([0x1000] * 8), 0x10000, head - 1, 1, 1, 8192, 128, 1, 0.1, 2, None) == -10
     limit[0] = 1 << 20
