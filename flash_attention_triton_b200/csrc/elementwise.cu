@@ -140,18 +140,16 @@ __global__ void __launch_bounds__(kPreThreads)
 // ----------------------------------------------------------------------------------------
 template <int D>
 struct PreRing {
-  static constexpr int kGroup = 128 / D;              // tiles per stage: 64 KiB of rows whatever D
-  static constexpr int kTileBytes = 128 * D * 2;      // one tensor's rows of one tile, padded width
-  static constexpr int kStageBytes = 2 * kGroup * kTileBytes;  // per tile: o, then dout
-  static constexpr int kStages = 3;
+  static constexpr int kTileBytes = 128 * D * 2;      // one tensor's rows at the padded width
+  static constexpr int kStageBytes = 2 * kTileBytes;  // o, then dout
+  static constexpr int kStages = D == 128 ? 3 : (D == 64 ? 6 : 8);
   static constexpr int kConsumers = 256;
   static constexpr int kThreads = kConsumers + 32;
-  // after the stages: full / empty barriers, two result buffers of kGroup x 256 floats, two of
-  // kGroup x 8 maxima
+  // after the stages: full / empty barriers, two result buffers of 256 floats, two of 8 maxima
   static constexpr int kOffBars = kStages * kStageBytes;
   static constexpr int kOffStat = kOffBars + 16 * kStages;
-  static constexpr int kOffMax = kOffStat + 2 * kGroup * 256 * 4;
-  static constexpr int kOffAbort = kOffMax + 2 * kGroup * 8 * 4;
+  static constexpr int kOffMax = kOffStat + 2 * 256 * 4;
+  static constexpr int kOffAbort = kOffMax + 2 * 8 * 4;
   static constexpr int kSmemBytes = kOffAbort + 16;
 };
 
@@ -179,7 +177,6 @@ __global__ void __launch_bounds__(PreRing<D>::kThreads, 1)
                                long long tiles, int d8, int H, Strides so, Strides sdo,
                                int* status) {
   using R = PreRing<D>;
-  constexpr int G = R::kGroup;
   constexpr int kLanesPerRow = D / 8;
   constexpr int kRowsPerPass = R::kConsumers / kLanesPerRow;  // 64, 32 or 16
   constexpr int kPasses = 128 / kRowsPerPass;                 // 2, 4 or 8
@@ -202,46 +199,33 @@ __global__ void __launch_bounds__(PreRing<D>::kThreads, 1)
   }
   __syncthreads();
   const uint32_t row_bytes = static_cast<uint32_t>(d8) * 16u;
-  // a stage holds the tiles G * group .. G * group + G - 1 (those that exist)
-  const long long groups = (tiles + G - 1) / G;
 
   if (warp == R::kConsumers / 32) {
     // ---------------- producer warp ----------------
     int it = 0;
-    for (long long group = blockIdx.x; group < groups; group += gridDim.x, ++it) {
+    for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
       const int s = it % R::kStages;
       const uint32_t ph = (it / R::kStages) & 1;
       if (!mbar_wait_warp(empty(s), ph ^ 1, w, kPSiteProducer)) break;
-      uint32_t total = 0;
-#pragma unroll
-      for (int j = 0; j < G; ++j) {
-        const long long tile = group * G + j;
-        if (tile < tiles) total += 2u * min(128, N - static_cast<int>(tile % ntiles) * 128) * row_bytes;
-      }
-      if (lane == 0) mbar_arrive_expect_tx(full(s), total);
+      const long long bh = tile / ntiles;
+      const int t = static_cast<int>(tile - bh * ntiles);
+      const long long bb = bh / H, hh = bh - bb * H;
+      const int rows = min(128, N - t * 128);
+      if (lane == 0) mbar_arrive_expect_tx(full(s), 2u * rows * row_bytes);
       __syncwarp();
+      const uint32_t dst = base + s * R::kStageBytes;
 #pragma unroll
-      for (int j = 0; j < G; ++j) {
-        const long long tile = group * G + j;
-        if (tile >= tiles) break;
-        const long long bh = tile / ntiles;
-        const int t = static_cast<int>(tile - bh * ntiles);
-        const long long bb = bh / H, hh = bh - bb * H;
-        const int rows = min(128, N - t * 128);
-        const uint32_t dst = base + s * R::kStageBytes + j * 2 * R::kTileBytes;
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          const Strides& st = which ? sdo : so;
-          const uint4* src = (which ? dout : o) + bb * st.b + hh * st.h +
-                             static_cast<long long>(t) * 128 * st.n;
-          const uint32_t d0 = dst + which * R::kTileBytes;
-          if (st.n == d8) {
-            if (lane == 0) bulk_load_1d(d0, src, rows * row_bytes, full(s));
-          } else {
-            for (int r = lane; r < rows; r += 32)
-              bulk_load_1d(d0 + r * row_bytes, src + static_cast<long long>(r) * st.n, row_bytes,
-                           full(s));
-          }
+      for (int which = 0; which < 2; ++which) {
+        const Strides& st = which ? sdo : so;
+        const uint4* src = (which ? dout : o) + bb * st.b + hh * st.h +
+                           static_cast<long long>(t) * 128 * st.n;
+        const uint32_t d0 = dst + which * R::kTileBytes;
+        if (st.n == d8) {
+          if (lane == 0) bulk_load_1d(d0, src, rows * row_bytes, full(s));
+        } else {
+          for (int r = lane; r < rows; r += 32)
+            bulk_load_1d(d0 + r * row_bytes, src + static_cast<long long>(r) * st.n, row_bytes,
+                         full(s));
         }
       }
     }
@@ -251,102 +235,90 @@ __global__ void __launch_bounds__(PreRing<D>::kThreads, 1)
   // ---------------- consumer warps ----------------
   const int sub = threadIdx.x % kLanesPerRow;
   const int row_in_pass = threadIdx.x / kLanesPerRow;
-  float lse_cur[G][kPasses], lse_nxt[G][kPasses];
-  auto fetch_lse = [&](long long group, float (*dst)[kPasses]) {
+  float lse_cur[kPasses], lse_nxt[kPasses];
+  auto fetch_lse = [&](long long tile, float* dst) {
+    const long long bh = tile / ntiles;
+    const int t = static_cast<int>(tile - bh * ntiles);
 #pragma unroll
-    for (int j = 0; j < G; ++j) {
-      const long long tile = group * G + j;
-      const long long bh = tile / ntiles;
-      const int t = static_cast<int>(tile - bh * ntiles);
-#pragma unroll
-      for (int i = 0; i < kPasses; ++i) {
-        const int row = t * 128 + i * kRowsPerPass + row_in_pass;
-        dst[j][i] = (sub == 0 && tile < tiles && row < N) ? __ldg(lse + bh * N + row) : INFINITY;
-      }
-    }
-  };
-  // the results of a group are complete in shared memory: one coalesced 1 KiB store per tile
-  auto write_out = [&](long long group, int pb) {
-#pragma unroll
-    for (int j = 0; j < G; ++j) {
-      const long long tile = group * G + j;
-      if (tile >= tiles) break;
-      rowstats[tile * 256 + threadIdx.x] = stat[(pb * G + j) * 256 + threadIdx.x];
-      if (threadIdx.x == 0) {
-        unsigned m = wmax[(pb * G + j) * 8];
-#pragma unroll
-        for (int i = 1; i < 8; ++i) m = max(m, wmax[(pb * G + j) * 8 + i]);
-        tile_amax[tile] = m;
-      }
+    for (int i = 0; i < kPasses; ++i) {
+      const int row = t * 128 + i * kRowsPerPass + row_in_pass;
+      dst[i] = (sub == 0 && tile < tiles && row < N) ? __ldg(lse + bh * N + row) : INFINITY;
     }
   };
   fetch_lse(blockIdx.x, lse_cur);
   int it = 0;
-  long long prev_group = -1;
-  for (long long group = blockIdx.x; group < groups; group += gridDim.x, ++it) {
+  long long prev_tile = -1;
+  for (long long tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++it) {
     const int s = it % R::kStages;
     const uint32_t ph = (it / R::kStages) & 1;
-    fetch_lse(group + gridDim.x, lse_nxt);
+    fetch_lse(tile + gridDim.x, lse_nxt);
     const bool ok = mbar_wait(full(s), ph, w, kPSiteConsumer);
     if (!consumers_all(ok, R::kConsumers)) return;
-    if (prev_group >= 0) write_out(prev_group, (it - 1) & 1);
-    const int cb = it & 1;
+    // the previous tile's results are complete in shared memory: one coalesced store
+    if (prev_tile >= 0) {
+      const int pb = (it - 1) & 1;
+      rowstats[prev_tile * 256 + threadIdx.x] = stat[pb * 256 + threadIdx.x];
+      if (threadIdx.x == 0) {
+        unsigned m = wmax[pb * 8];
 #pragma unroll
-    for (int j = 0; j < G; ++j) {
-      const long long tile = group * G + j;
-      if (tile < tiles) {  // uniform over the CTA
-        const int rows = min(128, N - static_cast<int>(tile % ntiles) * 128);
-        const uint4* so_ =
-            reinterpret_cast<const uint4*>(smem + s * R::kStageBytes + j * 2 * R::kTileBytes);
-        const uint4* sdo_ = so_ + R::kTileBytes / 16;
-        uint4 a[kPasses], b[kPasses];
-#pragma unroll
-        for (int i = 0; i < kPasses; ++i) {
-          const int r = i * kRowsPerPass + row_in_pass;
-          if (r < rows && sub < d8) {
-            a[i] = so_[r * d8 + sub];
-            b[i] = sdo_[r * d8 + sub];
-          } else {
-            a[i] = make_uint4(0, 0, 0, 0);
-            b[i] = make_uint4(0, 0, 0, 0);
-          }
-        }
-        if (j == G - 1 || tile + 1 >= tiles) {  // the stage's last pieces are in registers
-          __syncwarp();
-          if (lane == 0) mbar_arrive(empty(s));
-        }
-        unsigned amax2 = 0;
-#pragma unroll
-        for (int i = 0; i < kPasses; ++i) {
-          float acc = dot8<BF16>(a[i], b[i]);
-#pragma unroll
-          for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
-            acc += __shfl_xor_sync(0xffffffffu, acc, off);
-          amax2 = __vmaxu2(amax2, b[i].x & 0x7fff7fffu);
-          amax2 = __vmaxu2(amax2, b[i].y & 0x7fff7fffu);
-          amax2 = __vmaxu2(amax2, b[i].z & 0x7fff7fffu);
-          amax2 = __vmaxu2(amax2, b[i].w & 0x7fff7fffu);
-          const int r = i * kRowsPerPass + row_in_pass;
-          if (sub == 0) {
-            const bool valid = r < rows;
-            stat[(cb * G + j) * 256 + r] = valid ? -lse_cur[j][i] * kLog2e : -INFINITY;
-            stat[(cb * G + j) * 256 + 128 + r] = valid ? -acc : 0.f;
-          }
-        }
-        unsigned m = max(amax2 & 0xffffu, amax2 >> 16);
-        m = __reduce_max_sync(0xffffffffu, m);
-        if (lane == 0) wmax[(cb * G + j) * 8 + warp] = m;
+        for (int i = 1; i < 8; ++i) m = max(m, wmax[pb * 8 + i]);
+        tile_amax[prev_tile] = m;
       }
     }
+    const int t = static_cast<int>(tile % ntiles);
+    const int rows = min(128, N - t * 128);
+    const uint4* so_ = reinterpret_cast<const uint4*>(smem + s * R::kStageBytes);
+    const uint4* sdo_ = reinterpret_cast<const uint4*>(smem + s * R::kStageBytes + R::kTileBytes);
+    uint4 a[kPasses], b[kPasses];
 #pragma unroll
-    for (int j = 0; j < G; ++j)
+    for (int i = 0; i < kPasses; ++i) {
+      const int r = i * kRowsPerPass + row_in_pass;
+      if (r < rows && sub < d8) {
+        a[i] = so_[r * d8 + sub];
+        b[i] = sdo_[r * d8 + sub];
+      } else {
+        a[i] = make_uint4(0, 0, 0, 0);
+        b[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty(s));  // the pieces are in registers
+    unsigned amax2 = 0;
+    const int cb = it & 1;
 #pragma unroll
-      for (int i = 0; i < kPasses; ++i) lse_cur[j][i] = lse_nxt[j][i];
-    prev_group = group;
+    for (int i = 0; i < kPasses; ++i) {
+      float acc = dot8<BF16>(a[i], b[i]);
+#pragma unroll
+      for (int off = kLanesPerRow / 2; off > 0; off >>= 1)
+        acc += __shfl_xor_sync(0xffffffffu, acc, off);
+      amax2 = __vmaxu2(amax2, b[i].x & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].y & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].z & 0x7fff7fffu);
+      amax2 = __vmaxu2(amax2, b[i].w & 0x7fff7fffu);
+      const int r = i * kRowsPerPass + row_in_pass;
+      if (sub == 0) {
+        const bool valid = r < rows;
+        stat[cb * 256 + r] = valid ? -lse_cur[i] * kLog2e : -INFINITY;
+        stat[cb * 256 + 128 + r] = valid ? -acc : 0.f;
+      }
+    }
+    unsigned m = max(amax2 & 0xffffu, amax2 >> 16);
+    m = __reduce_max_sync(0xffffffffu, m);
+    if (lane == 0) wmax[cb * 8 + warp] = m;
+#pragma unroll
+    for (int i = 0; i < kPasses; ++i) lse_cur[i] = lse_nxt[i];
+    prev_tile = tile;
   }
-  if (prev_group >= 0) {
+  if (prev_tile >= 0) {
     named_bar_sync(1, R::kConsumers);
-    write_out(prev_group, (it - 1) & 1);
+    const int pb = (it - 1) & 1;
+    rowstats[prev_tile * 256 + threadIdx.x] = stat[pb * 256 + threadIdx.x];
+    if (threadIdx.x == 0) {
+      unsigned m = wmax[pb * 8];
+#pragma unroll
+      for (int i = 1; i < 8; ++i) m = max(m, wmax[pb * 8 + i]);
+      tile_amax[prev_tile] = m;
+    }
   }
 }
 
@@ -398,8 +370,7 @@ cudaError_t launch_pre_t(const AttnShape& s, const void* o, const Strides& so, c
     const cudaError_t attr = cudaFuncSetAttribute(
         kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, R::kSmemBytes);
     if (attr != cudaSuccess) return attr;
-    const long long groups = (tiles + R::kGroup - 1) / R::kGroup;
-    const unsigned grid = static_cast<unsigned>(groups < num_sms ? groups : num_sms);
+    const unsigned grid = static_cast<unsigned>(tiles < num_sms ? tiles : num_sms);
     kernel<<<grid, R::kThreads, R::kSmemBytes, stream>>>(
         static_cast<const uint4*>(o), static_cast<const uint4*>(dout), lse, rowstats, tile_amax,
         s.N, ntiles, tiles, s.Dg / 8, s.H, in_vec8(so), in_vec8(sdo), status);
