@@ -130,21 +130,24 @@ def _backward_mode(deterministic: bool, headdim: int, seqlen_q: int) -> int:
     """Which dQ strategy serves ``deterministic``.
 
     ``True`` must give the same bits whatever the batch / head partitioning, so the choice
-    depends on the sequence length only: the spill mode (fastest deterministic one) unless one
-    head's scratch is too large, then the recompute mode.  ``False`` (the reference's
-    default, atomics there) means "fastest": the spill mode where it beats the atomic kernel
-    (head dims above 64), the atomic kernel elsewhere.  ``FA2_B200_BWD_MODE`` = ``atomic`` /
-    ``recompute`` / ``spill`` overrides both (for experiments).
+    depends on the head dim and the sequence length only.  Head dims above 64: the spill mode
+    (fastest there, 12-15 % ahead of the recompute mode) unless one head's scratch is too
+    large, then the recompute mode.  Head dims up to 64: the recompute mode, which measures
+    within 4 % of the spill mode either way there (the 32 KiB dS tile does not shrink with the
+    head dim, the tensor work does) and needs no scratch, like the reference's O(N) backward.
+    ``False`` (the reference's default, atomics there) means "fastest": the atomic kernel at
+    head dims up to 64 (15-25 % ahead), the deterministic choice above.  ``FA2_B200_BWD_MODE`` =
+    ``atomic`` / ``recompute`` / ``spill`` overrides both (for experiments).
     """
     if headdim > 128:  # one (deterministic) backward exists there: scores + three consumers
         return _MODE_SPILL
     forced = os.environ.get("FA2_B200_BWD_MODE")
     if forced:
         return _MODE_NAMES[forced]
+    if headdim <= 64:
+        return _MODE_RECOMPUTE if deterministic else _MODE_ATOMIC
     scratch_ok = _scratch_bytes_per_head(seqlen_q, headdim) <= _SCRATCH_MAX_BYTES_PER_HEAD
-    if deterministic:
-        return _MODE_SPILL if scratch_ok else _MODE_RECOMPUTE
-    return _MODE_SPILL if scratch_ok and headdim > 64 else _MODE_ATOMIC
+    return _MODE_SPILL if scratch_ok else _MODE_RECOMPUTE
 
 
 def _allocate_workspace(lib, device, batch, nheads, seqlen_q, headdim, mode):

@@ -177,10 +177,13 @@ def test_backward_mode_choice_depends_on_the_sequence_length_only(monkeypatch):
 
     monkeypatch.delenv("FA2_B200_BWD_MODE", raising=False)
     assert api._backward_mode(True, 128, 8192) == api._MODE_SPILL
-    assert api._backward_mode(True, 32, 4095) == api._MODE_SPILL
+    assert api._backward_mode(True, 32, 4095) == api._MODE_RECOMPUTE     # no scratch at d <= 64: same speed
+    assert api._backward_mode(True, 64, 8192) == api._MODE_RECOMPUTE
+    assert api._backward_mode(True, 96, 8192) == api._MODE_SPILL
     assert api._backward_mode(True, 128, 32768) == api._MODE_SPILL       # 1 GiB of dS per head
     assert api._backward_mode(True, 128, 65536) == api._MODE_RECOMPUTE   # 4 GiB per head
     assert api._backward_mode(False, 128, 8192) == api._MODE_SPILL       # fastest at d = 128
+    assert api._backward_mode(False, 128, 65536) == api._MODE_RECOMPUTE  # ahead of the atomic kernel there
     assert api._backward_mode(False, 64, 8192) == api._MODE_ATOMIC
     assert api._backward_mode(False, 256, 8192) == api._MODE_SPILL       # the one backward there
     monkeypatch.setenv("FA2_B200_BWD_MODE", "recompute")

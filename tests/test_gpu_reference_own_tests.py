@@ -46,7 +46,7 @@ def test_reference_test_file_passes_unmodified():
     assert " failed" not in summary and " error" not in summary, tail
     assert int(re.search(r"(\d+) passed", summary).group(1)) >= 40, tail
     # Skips allowed: test_non_determinism where the default backward is deterministic (head dims
-    # above 64 run the spill mode, whose dQ has a fixed summation order, and on the smaller ones
+    # above 64 run the spill mode, whose dQ has a fixed summation order, and up to 64
     # the atomics may happen to land in one order; the reference words that skip itself).  Nothing
     # else may skip: in particular no resource limit (the reference's own default configuration
     # does not fit this GPU's tensor memory; this package's does).
