@@ -16,14 +16,17 @@ Printed JSON (one line, rank 0):
                tensors: host->device copies of q,k,v,dO and device->host copies of o,dq,dk,dv are
                inside the timed region, every step; copy-in, compute and copy-out of
                neighbouring steps overlap on three streams.
-  roofline     the backward-main call against the tensor roofline (achieved = its algorithmic
-               FLOPs / its average duration, peak = MEASURED_PEAKS.json bf16_tflops), and one entry
-               per kernel of the step: fwd, preprocess (HBM), bwd_dkdv_kernel, and
-               bwd_consume_kernel (HBM: it reads the spilled dS tiles) or bwd_dq_kernel.  Every
+  roofline     the dominant kernel of the step, bwd_dkdv_kernel (half of the step: 4 of the
+               backward's 5 tile products), against the tensor roofline (achieved = its
+               algorithmic FLOPs / its average duration, peak = MEASURED_PEAKS.json bf16_tflops),
+               then backward_call (both kernels of fa2_bwd together) and one entry per other
+               kernel: fwd, preprocess (HBM), and bwd_consume_kernel (HBM: it reads the spilled
+               dS tiles) or bwd_dq_kernel.  In the atomic mode and at head dim 256, where no
+               event separates the kernels of the call, the top level is the call.  Every
                duration comes from CUDA events recorded between the calls of the timed steps
                themselves (the one between the two backward kernels through fa2_bwd_mark_between),
                so sum_of_parts_ms = ms_per_step up to the event overhead.  traffic = DRAM bytes of
-               the backward-main kernels per step from an ncu capture (see NCU_BWD_DRAM_MB_PER_24).
+               the kernel per launch from an ncu capture (see NCU_DKDV_DRAM_MB_PER_24).
                At head dims 32 and 64 the entries carry softmax_ceiling (see softmax_ceiling).
   sustained    the same device-resident step run back to back for about a second under the
                clock sampler (the timed region is too short for NVML's clock averaging):
@@ -85,6 +88,7 @@ METRIC = "causal attn fwd+bwd TFLOP/s, bf16 N=8192 d=128"
 # pair 329.6 + 1679.5 MB (dK/dV, writes the dS tiles) plus 1744.1 + 46.2 MB (dQ, reads them back).
 NCU_BWD_DRAM_MB_PER_24 = {0: 381.8 + 209.7 + 100.7 + 20.1, 1: 203.2 + 76.1 + 204.3 + 36.8,
                           2: 329.6 + 1679.5 + 1744.1 + 46.2}
+NCU_DKDV_DRAM_MB_PER_24 = {1: 203.2 + 76.1, 2: 329.6 + 1679.5}  # the dK/dV kernel alone
 
 # Polynomial share of the exponentials (of every 8 column pairs) the kernels are built with
 # (FA2_FWD_POLY_PAIRS_PER_8 in csrc/fwd.cu, FA2_BWD_POLY_PAIRS_PER_8 in csrc/bwd_roles.cuh).
@@ -502,31 +506,50 @@ def main():
         top = c["frac_of_tensor_peak"] * peaks["bf16"]
         return {"bound": "exp", "softmax_ceiling": {**c, "tflops": top, "frac": tf / top}}
 
-    roofline = {
-        "kernel": "bwd_scores_wide_kernel + bwd_consume_kernel x3 (dV, dK, dQ)" if d > 128 else (
-            "bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert",
-            "bwd_dkdv_kernel + bwd_dq_kernel (S, dP recomputed)",
-            "bwd_dkdv_kernel (dS tiles spilled) + bwd_consume_kernel (dQ)")[mode],
-        "bound": "tensor", "peak": peaks["bf16"], "unit": "TFLOP/s", **tensor(bwd_tf),
-        "peak_source": f"{peaks['source']} burst bf16 GEMM; frac_of_sustained uses the sustained one",
-        "timing": "CUDA events between the calls of the timed steps themselves: fwd + pre + bwd = ms_per_step",
+    call_names = ("bwd_dkdv_kernel (fused dQ atomics) + memset + dq_convert",
+                  "bwd_dkdv_kernel + bwd_dq_kernel (S, dP recomputed)",
+                  "bwd_dkdv_kernel (dS tiles spilled) + bwd_consume_kernel (dQ)")
+    backward_call = {
+        "kernels": "bwd_scores_wide_kernel + bwd_consume_kernel x3 (dV, dK, dQ)" if d > 128 else call_names[mode],
+        **tensor(bwd_tf), "ms": ms_bwd, "algorithmic_flops": 2.5 * my_fwd_flops,
         "traffic": traffic_bytes(d, mode, lb * lh, n),
-        "traffic_note": "dram__bytes_read+write of the backward-main kernel(s) per step, from an ncu capture of "
-                        "24 batch*head problems (d=128, N=8192) scaled by batch*head; null for other shapes",
-        "algorithmic_flops": 2.5 * my_fwd_flops,
+    }
+    # The top level is the DOMINANT kernel of the step.  Where the backward call is two kernels
+    # and the event between them exists, that is bwd_dkdv_kernel (4 of the backward's 5 tile
+    # products; about half of the step), else the backward call as a whole.
+    split_bwd = "bwd_first" in parts and d <= 128
+    pad_d = 32 if d <= 32 else 64 if d <= 64 else 128
+    if split_bwd:
+        t1, t2 = parts["bwd_first"], parts["bwd_second"]
+        dkdv_flops = 0.8 * 2.5 * my_fwd_flops
+        dkdv_tf = dkdv_flops / (t1 * 1e-3) / 1e12
+        top = {"kernel": "bwd_dkdv_kernel<%d, %s, %s>" % (pad_d, "bf16" if code else "fp16", ("", "plain", "spill")[mode]),
+               **tensor(dkdv_tf), "ms": t1, "algorithmic_flops": dkdv_flops,
+               "share_of_step": t1 / ms_per_step,
+               "traffic": NCU_DKDV_DRAM_MB_PER_24.get(mode) and (
+                   NCU_DKDV_DRAM_MB_PER_24[mode] * 1e6 * lb * lh / 24.0 if (d, n) == (128, 8192) else None),
+               **ceiling("bwd", dkdv_tf)}
+    else:
+        top = {"kernel": backward_call["kernels"], **tensor(bwd_tf), "ms": ms_bwd,
+               "algorithmic_flops": 2.5 * my_fwd_flops, "share_of_step": ms_bwd / ms_per_step,
+               "traffic": backward_call["traffic"]}
+    roofline = {
+        "bound": "tensor", "peak": peaks["bf16"], "unit": "TFLOP/s", **top,
+        "peak_source": f"{peaks['source']} burst bf16 GEMM; frac_of_sustained uses the sustained one",
+        "timing": "CUDA events between the calls of the timed steps themselves (and between the two kernels of the "
+                  "backward call): fwd + pre + bwd = ms_per_step",
+        "traffic_note": "dram__bytes_read+write of this kernel per launch, from an ncu capture of 24 batch*head "
+                        "problems (d=128, N=8192) scaled by batch*head; null for other shapes",
+        "backward_call": backward_call,
         "fwd": {**tensor(fwd_tf), "ms": ms_fwd, **ceiling("fwd", fwd_tf)},
         "bwd_ms": ms_bwd,
         "preprocess": hbm(pre_bytes, ms_pre),
         "sum_of_parts_ms": ms_fwd + ms_pre + ms_bwd,
     }
-    if "bwd_first" in parts and d <= 128:
-        # dK/dV kernel: 4 of the 5 tile products of the backward; second kernel: the fifth (spill:
-        # bound by reading the 32 KiB dS tile and the K tile per product) or, recomputing, 3 more
-        t1, t2 = parts["bwd_first"], parts["bwd_second"]
+    if split_bwd:
+        # second kernel: the fifth tile product (spill: bound by reading the 32 KiB dS tile and
+        # the K tile per product) or, recomputing, 3 products and the exponentials
         tiles = (n + 127) // 128
-        dkdv_tf = 0.8 * 2.5 * my_fwd_flops / (t1 * 1e-3) / 1e12
-        roofline["bwd_dkdv_kernel"] = {**tensor(dkdv_tf), "ms": t1, "algorithmic_flops": 0.8 * 2.5 * my_fwd_flops,
-                                       **ceiling("bwd", dkdv_tf)}
         if mode == 2:
             scratch = lb * lh * tiles * (tiles + 1) // 2 * 32768
             roofline["bwd_consume_kernel"] = {

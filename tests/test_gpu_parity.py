@@ -272,6 +272,40 @@ def test_lse_and_rowstats_through_the_c_abi():
     assert torch.equal(tile_amax, want_amax)
 
 
+@pytest.mark.parametrize("d, strided", [(32, False), (48, True), (64, True), (128, False), (128, True), (256, False)])
+def test_preprocess_over_many_tiles_per_sm(d, strided):
+    """fa2_bwd_preprocess on more tiles than one pass of the persistent CTAs covers (every CTA
+    walks several tiles and its ring of stages wraps), ragged N, head dims below their padded
+    width, rows contiguous (one bulk copy per tile) and strided (`[B, N, H, d]`: one per row)."""
+    b, h, n = 3, 8, 128 * 39 + 77  # 3 * 8 * 40 = 960 tiles on 148 SMs
+    g = torch.Generator().manual_seed(11)
+    o = torch.randn(b, h, n, d, generator=g).to(torch.float16)
+    do = (torch.randn(b, h, n, d, generator=g) * 3e-3).to(torch.float16)
+    lse = torch.randn(b, h, n, generator=g).to(DEV)
+    if strided:
+        od, dod = (t.transpose(1, 2).contiguous().to(DEV).transpose(1, 2) for t in (o, do))
+    else:
+        od, dod = o.to(DEV), do.to(DEV)
+    lib = _lib.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    rs = torch.full((lib.fa2_rowstats_bytes(b, h, n) // 4,), float("nan"), device=DEV)
+    assert lib.fa2_bwd_preprocess_strided(od.data_ptr(), dod.data_ptr(), lse.data_ptr(), rs.data_ptr(),
+                                          b, h, n, d, 0, _lib.stride_array(od, dod), st) == 0
+    assert _lib.device_status() == 0
+    t = 40
+    tile_amax = rs[b * h * t * 256:].cpu().view(torch.int32).view(b * h, t)
+    rs = rs[: b * h * t * 256].view(b * h, t, 2, 128).cpu()
+    lse2 = -rs[:, :, 0].reshape(b * h, t * 128)
+    delta = -rs[:, :, 1].reshape(b * h, t * 128)
+    want_delta = (o.double() * do.double()).sum(-1).reshape(b * h, n)
+    assert (delta[:, :n].double() - want_delta).abs().max() < 1e-5 * max(1.0, want_delta.abs().max().item())
+    assert (lse2[:, :n].double() - lse.cpu().double().reshape(b * h, n) * math.log2(math.e)).abs().max() < 1e-5
+    assert torch.isinf(lse2[:, n:]).all() and (delta[:, n:] == 0).all()
+    want_amax = torch.nn.functional.pad(do.abs().reshape(b * h, n, d), (0, 0, 0, t * 128 - n))
+    want_amax = want_amax.reshape(b * h, t, 128 * d).amax(-1).view(torch.int16).to(torch.int32)
+    assert torch.equal(tile_amax, want_amax)
+
+
 def test_fp32_inputs_follow_the_reference_dtype_policy():
     """fp32 in -> computed in fp16, output and grads returned as fp32 (flash_attention_2.py:316,339);
     the reference's own tests use fp32 inputs with atol 1e-2 on O (tests/test_flash_attention_2.py:297)."""
