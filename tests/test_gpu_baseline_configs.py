@@ -14,20 +14,22 @@ four (batch, head) problems are compared
   conftest.RMS_FACTOR_VS_REFERENCE of the reference's (1.25 for fp16; 2.0 for bf16, see there),
   maximum within conftest.MAX_FACTOR_VS_REFERENCE (or inside the flat bound).
 
-The numbers are printed and, when the directory exists, written to
-``gpurun_out/parity_<config>.json``.
+The numbers are printed and, when the environment variable ``FA2_B200_REPORT_DIR`` names a
+directory, written to ``parity_<config>.json`` there.
 """
 
 from __future__ import annotations
 
 import json
 import math
+import os
+from pathlib import Path
 
 import numpy as np
 import pytest
 import torch
 
-from conftest import (BASE_TOL, MAX_FACTOR_VS_REFERENCE, RMS_FACTOR_VS_REFERENCE, ROOT, elementwise_tolerance, error_stats,
+from conftest import (BASE_TOL, MAX_FACTOR_VS_REFERENCE, RMS_FACTOR_VS_REFERENCE, elementwise_tolerance, error_stats,
                       make_inputs)
 from flash_attention_triton_b200 import _lib, flash_attention_v2
 from oracle.attention_oracle import naive_attention, reference_tiled
@@ -88,9 +90,9 @@ def test_error_at_full_size_against_oracle_and_reference_arithmetic(name):
     for key, w in worst.items():
         print(f"  {key}: max-abs ours {w['max_ours']:.3e} ref {w['max_ref']:.3e} | "
               f"rms ours {w['rms_ours']:.3e} ref {w['rms_ref']:.3e}")
-    out_dir = ROOT / "gpurun_out"
-    if out_dir.is_dir():
-        (out_dir / f"parity_{name}.json").write_text(json.dumps({"worst": worst, "rows": rows}, indent=1))
+    out_dir = os.environ.get("FA2_B200_REPORT_DIR")
+    if out_dir and os.path.isdir(out_dir):
+        (Path(out_dir) / f"parity_{name}.json").write_text(json.dumps({"worst": worst, "rows": rows}, indent=1))
     problems = []
     for row in rows:
         tag = f"{row['tensor']}[{row['b']},{row['h']}]"
