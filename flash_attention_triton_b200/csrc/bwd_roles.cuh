@@ -16,13 +16,21 @@
 
 namespace fa2 {
 
-// 2^x for column pair `c` (compile-time index after unrolling): a fixed share of the pairs
-// goes to the FMA-pipe polynomial, the rest to the MUFU, because 128 x 128 exponentials per
-// tile pair would otherwise keep the MUFU (16 / clk / SM) busy for 1024 cycles.
+// 2^x for column pair `c` (compile-time index after unrolling): SHARE of every 8 pairs go to
+// the FMA-pipe polynomial, the rest to the MUFU, because 128 x 128 exponentials per tile pair
+// would otherwise keep the MUFU (16 / clk / SM) busy for 1024 cycles.
+template <int SHARE = FA2_BWD_POLY_PAIRS_PER_8>
 __device__ __forceinline__ float2 exp2_pair(float2 x, int c) {
-  if ((c & 7) < FA2_BWD_POLY_PAIRS_PER_8) return ex2_poly2(x);
+  if ((c & 7) < SHARE) return ex2_poly2(x);
   return make_float2(ex2(x.x), ex2(x.y));
 }
+// Share used by the transposed-score kernels.  At head dims up to 64 the tensor pipe has time to
+// spare and the compute warps' instruction stream is what a tile pair waits for, so fewer
+// exponentials go to the (longer) polynomial: measured on the fused-atomics kernel 6-8 % faster
+// with 2 than with 4, the other modes within 3 % either way.  A function of the head dim only, so
+// that P, and with it dK and dV, have the same bits in every mode.
+template <int D>
+constexpr int kPolyShareT = D <= 64 ? 2 : FA2_BWD_POLY_PAIRS_PER_8;
 
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c),
@@ -34,6 +42,7 @@ __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, 
 // row and 64 q columns of a tile.  probabilities_of_row: p = 2^(s * c - lse2[q]) from the raw
 // scores `sr` and the negated, log2-scaled row statistics of the 64 columns (`nlse`, read with
 // warp-wide broadcasts).  mask_row: keep only the q columns >= `first` (128 keeps nothing).
+template <int SHARE = FA2_BWD_POLY_PAIRS_PER_8>
 __device__ __forceinline__ void probabilities_of_row(const uint32_t (&sr)[64], const float4* nlse,
                                                      float2 sc2, float2 (&p)[32]) {
 #pragma unroll
@@ -45,8 +54,8 @@ __device__ __forceinline__ void probabilities_of_row(const uint32_t (&sr)[64], c
     const float2 t1 = __ffma2_rn(
         make_float2(__uint_as_float(sr[4 * c4 + 2]), __uint_as_float(sr[4 * c4 + 3])), sc2,
         make_float2(l.z, l.w));
-    p[2 * c4] = exp2_pair(t0, 2 * c4);
-    p[2 * c4 + 1] = exp2_pair(t1, 2 * c4 + 1);
+    p[2 * c4] = exp2_pair<SHARE>(t0, 2 * c4);
+    p[2 * c4 + 1] = exp2_pair<SHARE>(t1, 2 * c4 + 1);
   }
 }
 __device__ __forceinline__ void mask_row(float2 (&p)[32], int first_column, int column0) {
@@ -447,7 +456,7 @@ __device__ __forceinline__ void dkdv_roles(
         tmem_ld_x32(tSt, sr);
         tmem_ld_x32(tSt + 32, sr + 32);
         tmem_wait_ld();
-        probabilities_of_row(sr, nlse, sc2, p);
+        probabilities_of_row<kPolyShareT<D>>(sr, nlse, sc2, p);
       }
       if (qt == jt || kv_ragged) {
         // diagonal tile: keep q >= kv; rows beyond the last key (zero-filled K, V) keep nothing,
