@@ -92,7 +92,7 @@ NCU_DKDV_DRAM_MB_PER_24 = {1: 203.2 + 76.1, 2: 329.6 + 1679.5}  # the dK/dV kern
 
 # Polynomial share of the exponentials (of every 8 column pairs) the kernels are built with
 # (FA2_FWD_POLY_PAIRS_PER_8 in csrc/fwd.cu, FA2_BWD_POLY_PAIRS_PER_8 in csrc/bwd_roles.cuh).
-POLY_SHARE = {"fwd": 3 / 8, "bwd": 4 / 8}
+POLY_SHARE = {"fwd": 3 / 8, "bwd": 2 / 8}  # at the head dims the ceiling is reported for (<= 64)
 
 
 def softmax_ceiling(d, which):
