@@ -458,7 +458,9 @@ __global__ void __launch_bounds__(kFwdThreads, 1)
             tma_store_4d(&to, ch * T::kChunkElems, qt * 128 + row0, hc,
                          smem_u32(sO + ch * T::kChunkTileBytes + row0 * T::kRowBytes));
           tma_store_commit();
-          tma_store_wait_all();
+          // the staging buffer may be refilled once the store has READ it; the write itself
+          // completes on its own before the grid does
+          tma_store_wait_read();
         }
       }
       const int row = qt * 128 + r;
