@@ -84,11 +84,11 @@ METRIC = "causal attn fwd+bwd TFLOP/s, bf16 N=8192 d=128"
 
 # DRAM bytes (read + write) of the backward-main kernels measured by ncu on the reduced C3
 # workload (24 batch*head problems, N=8192, d=128): fused kernel 381.8 + 209.7 MB and the convert
-# 100.7 + 20.1 MB; the recompute pair 203.2 + 76.1 MB (dK/dV) plus 204.3 + 36.8 MB (dQ); the spill
+# 100.7 + 20.1 MB; the recompute pair 208.6 + 74.7 MB (dK/dV) plus 204.3 + 36.8 MB (dQ); the spill
 # pair 329.6 + 1679.5 MB (dK/dV, writes the dS tiles) plus 1744.1 + 46.2 MB (dQ, reads them back).
-NCU_BWD_DRAM_MB_PER_24 = {0: 381.8 + 209.7 + 100.7 + 20.1, 1: 203.2 + 76.1 + 204.3 + 36.8,
+NCU_BWD_DRAM_MB_PER_24 = {0: 381.8 + 209.7 + 100.7 + 20.1, 1: 208.6 + 74.7 + 204.3 + 36.8,
                           2: 329.6 + 1679.5 + 1744.1 + 46.2}
-NCU_DKDV_DRAM_MB_PER_24 = {1: 203.2 + 76.1, 2: 329.6 + 1679.5}  # the dK/dV kernel alone
+NCU_DKDV_DRAM_MB_PER_24 = {1: 208.6 + 74.7, 2: 329.6 + 1679.5}  # the dK/dV kernel alone
 
 # Polynomial share of the exponentials (of every 8 column pairs) the kernels are built with
 # (FA2_FWD_POLY_PAIRS_PER_8 in csrc/fwd.cu, FA2_BWD_POLY_PAIRS_PER_8 in csrc/bwd_roles.cuh).
